@@ -1,0 +1,108 @@
+// Shared helpers of the hand-written sm_100a kernels: element conversion,
+// warp/block reductions, the C ABI conventions.
+//
+// Every exported function is `extern "C"`, takes raw device pointers and a
+// cudaStream_t, launches on that stream and returns the launch's cudaError_t
+// as an int (0 = success).  Sizes are validated by the Python wrappers, which
+// raise before anything is launched; the functions re-check what would make
+// a kernel read out of bounds and return cudaErrorInvalidValue instead of
+// launching.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TQ_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes of the C ABI
+#define TQ_F32 0
+#define TQ_BF16 1
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Number of elements of T in a 16-byte vector.
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+// Loads 16 bytes of T from `p` (16-byte aligned) and widens to float.
+template <typename T> __device__ __forceinline__ void load16_f32(const T* p, float* out);
+template <> __device__ __forceinline__ void load16_f32<float>(const float* p, float* out) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+template <> __device__ __forceinline__ void load16_f32<bf16>(const bf16* p, float* out) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// Loads two consecutive elements (4- or 8-byte aligned) and widens to float.
+template <typename T> __device__ __forceinline__ float2 load2_f32(const T* p);
+template <> __device__ __forceinline__ float2 load2_f32<float>(const float* p) {
+    return *reinterpret_cast<const float2*>(p);
+}
+template <> __device__ __forceinline__ float2 load2_f32<bf16>(const bf16* p) {
+    uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <typename T> __device__ __forceinline__ void store2_f32(T* p, float a, float b);
+template <> __device__ __forceinline__ void store2_f32<float>(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+template <> __device__ __forceinline__ void store2_f32<bf16>(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `red` holds 32 floats of shared
+// memory.  Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float r = (lane < nw) ? red[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float r = (lane < nw) ? red[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+static inline int tq_launch_status() { return (int)cudaGetLastError(); }

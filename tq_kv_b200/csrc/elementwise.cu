@@ -1,0 +1,254 @@
+// Memory-bound kernels around the matrix products: embedding gather, RMS
+// norm, bias + rotary position encoding + cache append, SwiGLU gating.
+// All arithmetic is float32; T* parameters are float or bfloat16.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: out[t, :] = float(table[tokens[t], :])
+// (src/models/turbo_generic.rs:1958 — a row gather, no scaling.)
+// A token id outside [0, V) writes zeros and raises bit 0 of *status.
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                             float* __restrict__ out, int H, int V, int* status) {
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    float* o = out + (size_t)t * H;
+    if (id < 0 || id >= V) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        if (threadIdx.x == 0 && status) atomicOr(status, 1);
+        return;
+    }
+    const TW* row = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32<TW>(row[i]);
+}
+
+TQ_API int tq_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int H, int V,
+                    int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == TQ_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, H, V, status);
+    else if (table_dtype == TQ_BF16)
+        embed_kernel<bf16><<<n_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, out, H, V, status);
+    else
+        return (int)cudaErrorInvalidValue;
+    return tq_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// RMS norm: y = x / sqrt(mean(x^2) + eps) * w, all in float32
+// (src/models/turbo_generic.rs:41-51).  x is the float32 residual stream;
+// `rows` (optional) selects the input rows, so that the final norm touches
+// only the rows whose logits are wanted.
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                               const int* __restrict__ rows, int H, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rms = sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>((xr[i] / rms) * w[i]);
+}
+
+TQ_API int tq_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int n_rows, int H,
+                      float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (out_dtype == TQ_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, (float*)out, rows, H, eps);
+    else if (out_dtype == TQ_BF16)
+        rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, w, (bf16*)out, rows, H, eps);
+    else
+        return (int)cudaErrorInvalidValue;
+    return tq_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Bias + rotate-half rotary encoding + head split + cache append.
+//
+// qkv: [T, (nh + 2*nkv) * hd] — q heads, then k heads, then v heads, each
+// head-major (src/models/turbo_generic.rs:815-817).  Bias is added first
+// (:805-813), then q and k are rotated (:417-427):
+//   out[:half] = x0*cos - x1*sin, out[half:] = x0*sin + x1*cos
+// over the first `rot` dims of a head (half = rot/2), with cos/sin rows taken
+// at the token's absolute position from tables [positions, rot/2] (:746-768).
+// q goes to q_out [T, nh*hd]; k and v go to the packed outputs (if given)
+// and into the paged cache (if given): position p of step row b lands in
+// logical page p / page_tokens (modulo ring_pages if > 0) at row
+// p % page_tokens.  In a ring, only the last ring_pages*page_tokens positions
+// of a sequence are written, so that no two tokens of one step meet in a row.
+// ---------------------------------------------------------------------------
+template <typename TI, typename TC>
+__global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* __restrict__ bias,
+                                      const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                      const int* __restrict__ new_lens, const int* __restrict__ block_table,
+                                      int table_width, int ring_pages, int page_tokens, TC* __restrict__ q_out,
+                                      TC* __restrict__ k_out, TC* __restrict__ v_out, TC* __restrict__ k_pages,
+                                      TC* __restrict__ v_pages, int nh, int nkv, int hd, int rot) {
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int b = tok_seq[t];
+    const int half = rot >> 1;
+    const int width = (nh + 2 * nkv) * hd;
+    const TI* x = qkv + (size_t)t * width;
+    const float* cs = cos_tab + (size_t)pos * half;
+    const float* sn = sin_tab + (size_t)pos * half;
+
+    // where this token's key/value row lives in the cache (or nowhere)
+    size_t cache_row = 0;
+    bool to_cache = k_pages != nullptr;
+    if (to_cache) {
+        int lp = pos / page_tokens;
+        if (ring_pages > 0) {
+            if (pos < new_lens[b] - ring_pages * page_tokens) to_cache = false;
+            lp %= ring_pages;
+        }
+        if (to_cache) {
+            const int page = block_table[(size_t)b * table_width + lp];
+            cache_row = ((size_t)page * nkv) * page_tokens + (pos % page_tokens);  // + g*page_tokens per head
+        }
+    }
+
+    // rotated part of q and k: one thread per (head, j < half)
+    const int n_rot = (nh + nkv) * half;
+    for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+        const int head = i / half, j = i - head * half;
+        const int c0 = head * hd + j, c1 = c0 + half;
+        float x0 = to_f32<TI>(x[c0]), x1 = to_f32<TI>(x[c1]);
+        if (bias) { x0 += bias[c0]; x1 += bias[c1]; }
+        const float c = cs[j], s = sn[j];
+        const float r0 = x0 * c - x1 * s;
+        const float r1 = x0 * s + x1 * c;
+        if (head < nh) {
+            TC* q = q_out + (size_t)t * nh * hd + head * hd;
+            q[j] = from_f32<TC>(r0);
+            q[j + half] = from_f32<TC>(r1);
+        } else {
+            const int g = head - nh;
+            if (k_out) {
+                TC* k = k_out + ((size_t)t * nkv + g) * hd;
+                k[j] = from_f32<TC>(r0);
+                k[j + half] = from_f32<TC>(r1);
+            }
+            if (to_cache) {
+                TC* k = k_pages + (cache_row + (size_t)g * page_tokens) * hd;
+                k[j] = from_f32<TC>(r0);
+                k[j + half] = from_f32<TC>(r1);
+            }
+        }
+    }
+    // dims beyond the rotated part of q and k pass through
+    if (rot < hd) {
+        const int rest = hd - rot;
+        for (int i = threadIdx.x; i < (nh + nkv) * rest; i += blockDim.x) {
+            const int head = i / rest, d = rot + (i - head * rest);
+            const int c = head * hd + d;
+            float v = to_f32<TI>(x[c]);
+            if (bias) v += bias[c];
+            if (head < nh) {
+                q_out[(size_t)t * nh * hd + c] = from_f32<TC>(v);
+            } else {
+                const int g = head - nh;
+                if (k_out) k_out[((size_t)t * nkv + g) * hd + d] = from_f32<TC>(v);
+                if (to_cache) k_pages[(cache_row + (size_t)g * page_tokens) * hd + d] = from_f32<TC>(v);
+            }
+        }
+    }
+    // values: bias only
+    const int v0 = (nh + nkv) * hd;
+    for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
+        const int g = i / hd, d = i - g * hd;
+        float v = to_f32<TI>(x[v0 + i]);
+        if (bias) v += bias[v0 + i];
+        if (v_out) v_out[(size_t)t * nkv * hd + i] = from_f32<TC>(v);
+        if (to_cache) v_pages[(cache_row + (size_t)g * page_tokens) * hd + d] = from_f32<TC>(v);
+    }
+}
+
+TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, const float* cos_tab,
+                             const float* sin_tab, const int* tok_pos, const int* tok_seq, const int* new_lens,
+                             const int* block_table, int table_width, int ring_pages, int page_tokens, void* q_out,
+                             void* k_out, void* v_out, void* k_pages, void* v_pages, int cache_dtype, int n_tokens,
+                             int nh, int nkv, int hd, int rot, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (rot <= 0 || rot > hd || (rot & 1) || page_tokens <= 0) return (int)cudaErrorInvalidValue;
+    if ((k_pages == nullptr) != (v_pages == nullptr)) return (int)cudaErrorInvalidValue;
+    if (k_pages && !block_table) return (int)cudaErrorInvalidValue;
+    const int threads = 128;
+#define TQ_LAUNCH(TI, TC)                                                                                       \
+    qkv_rope_cache_kernel<TI, TC><<<n_tokens, threads, 0, stream>>>(                                           \
+        (const TI*)qkv, bias, cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width,          \
+        ring_pages, page_tokens, (TC*)q_out, (TC*)k_out, (TC*)v_out, (TC*)k_pages, (TC*)v_pages, nh, nkv, hd, rot)
+    if (in_dtype == TQ_F32 && cache_dtype == TQ_F32) TQ_LAUNCH(float, float);
+    else if (in_dtype == TQ_F32 && cache_dtype == TQ_BF16) TQ_LAUNCH(float, bf16);
+    else if (in_dtype == TQ_BF16 && cache_dtype == TQ_BF16) TQ_LAUNCH(bf16, bf16);
+    else return (int)cudaErrorInvalidValue;
+#undef TQ_LAUNCH
+    return tq_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU gating: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(x) = x * sigmoid(x)
+// (src/models/turbo_generic.rs:105-110, :64-66).  gu holds the gate columns
+// first, then the up columns.
+// ---------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void swiglu_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        const float g = to_f32<TI>(gu[t * 2 * I + i]);
+        const float u = to_f32<TI>(gu[t * 2 * I + I + i]);
+        const float s = g / (1.f + expf(-g));
+        out[idx] = from_f32<TO>(s * u);
+    }
+}
+
+TQ_API int tq_swiglu(const void* gu, int in_dtype, void* out, int out_dtype, int n_rows, int I, cudaStream_t stream) {
+    const size_t total = (size_t)n_rows * I;
+    if (total == 0) return 0;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+#define TQ_LAUNCH(TI, TO) \
+    swiglu_kernel<TI, TO><<<(int)blocks, threads, 0, stream>>>((const TI*)gu, (TO*)out, I, total)
+    if (in_dtype == TQ_F32 && out_dtype == TQ_F32) TQ_LAUNCH(float, float);
+    else if (in_dtype == TQ_F32 && out_dtype == TQ_BF16) TQ_LAUNCH(float, bf16);
+    else if (in_dtype == TQ_BF16 && out_dtype == TQ_BF16) TQ_LAUNCH(bf16, bf16);
+    else return (int)cudaErrorInvalidValue;
+#undef TQ_LAUNCH
+    return tq_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// acc[i] += float(x[i]) — the residual sum in float32 when a library matrix
+// product produced the addend.
+// ---------------------------------------------------------------------------
+template <typename TI>
+__global__ void add_into_kernel(float* __restrict__ acc, const TI* __restrict__ x, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        acc[idx] += to_f32<TI>(x[idx]);
+}
+
+TQ_API int tq_add_into(float* acc, const void* x, int in_dtype, size_t total, cudaStream_t stream) {
+    if (total == 0) return 0;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (in_dtype == TQ_F32) add_into_kernel<float><<<(int)blocks, threads, 0, stream>>>(acc, (const float*)x, total);
+    else if (in_dtype == TQ_BF16) add_into_kernel<bf16><<<(int)blocks, threads, 0, stream>>>(acc, (const bf16*)x, total);
+    else return (int)cudaErrorInvalidValue;
+    return tq_launch_status();
+}

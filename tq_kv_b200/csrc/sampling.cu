@@ -1,0 +1,254 @@
+// Token selection from float32 logits on the device: arg-max, or
+// temperature + top-k + top-p with one uniform draw per row, with an
+// optional repeat penalty driven by per-row occurrence counts.
+//
+// Reference: src/engine.rs:353-360 (temperature <= 0 -> arg-max, else top-k
+// then top-p at the temperature), :403-419 (repeat penalty: once per
+// occurrence of a generated token, l > 0 ? l / p : l * p).  The sampler proper
+// is outside the reference's tree; the rules here are this project's:
+//  * arg-max ties go to the lowest token id;
+//  * top-k keeps every token whose logit is >= the k-th largest;
+//  * top-p walks the kept tokens by descending probability and keeps every
+//    token whose probability is >= that of the token at which the running
+//    mass first reaches top_p * (kept mass);
+//  * the draw walks the kept tokens in token-id order and takes the first
+//    one whose running mass exceeds u * (kept mass).
+// Probabilities are float32 exponentials, masses are summed in float64.
+#include "common.cuh"
+
+#define SAMPLE_THREADS 1024
+
+__device__ __forceinline__ float penalised(const float* logits, const int* counts, float penalty, int i) {
+    float l = logits[i];
+    if (counts) {
+        for (int c = counts[i]; c > 0; --c) l = l > 0.f ? l / penalty : l * penalty;
+    }
+    return l;
+}
+
+// order-preserving map float -> uint32 (larger float, larger key)
+__device__ __forceinline__ uint32_t order_key(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct ArgMax { float v; int i; };
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__device__ ArgMax block_argmax(ArgMax a, ArgMax* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax b{__shfl_xor_sync(0xffffffffu, a.v, o), __shfl_xor_sync(0xffffffffu, a.i, o)};
+        a = better(a, b);
+    }
+    __syncthreads();
+    if (lane == 0) red[warp] = a;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    ArgMax r = lane < nw ? red[lane] : ArgMax{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax b{__shfl_xor_sync(0xffffffffu, r.v, o), __shfl_xor_sync(0xffffffffu, r.i, o)};
+        r = better(r, b);
+    }
+    return r;
+}
+
+__device__ double block_sum_f64(double v, double* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum_f64(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    double r = lane < nw ? red[lane] : 0.0;
+    return warp_sum_f64(r);
+}
+
+// One block per row.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature, int top_k, float top_p,
+              const float* __restrict__ uniforms, int* __restrict__ counts, float penalty, int* __restrict__ out) {
+    __shared__ ArgMax red_am[32];
+    __shared__ double red_d[32];
+    __shared__ int hist_i[256];
+    __shared__ double hist_d[256];
+    __shared__ double seg_sum[SAMPLE_THREADS];
+    __shared__ uint32_t sh_prefix;
+    __shared__ double sh_remaining;
+    __shared__ int sh_token;
+
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* lg = logits + (size_t)row * ld;
+    int* cnt = counts ? counts + (size_t)row * V : nullptr;
+
+    // ---- arg-max (also the softmax's maximum) ----
+    ArgMax am{-INFINITY, 0x7fffffff};
+    for (int i = tid; i < V; i += blockDim.x) am = better(am, ArgMax{penalised(lg, cnt, penalty, i), i});
+    am = block_argmax(am, red_am);
+    if (temperature <= 0.f) {
+        if (tid == 0) {
+            out[row] = am.i;
+            if (cnt) cnt[am.i] += 1;
+        }
+        return;
+    }
+    const float mx = am.v;
+
+    // ---- top-k: key of the k-th largest logit by radix select ----
+    uint32_t kth_key = 0;   // keep everything
+    if (top_k > 0 && top_k < V) {
+        uint32_t prefix = 0, mask = 0;
+        int remaining = top_k;
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            if (tid < 256) hist_i[tid] = 0;
+            __syncthreads();
+            for (int i0 = 0; i0 < V; i0 += blockDim.x) {
+                const int i = i0 + tid;
+                int bin = -1;
+                if (i < V) {
+                    const uint32_t key = order_key(penalised(lg, cnt, penalty, i));
+                    if ((key & mask) == prefix) bin = (key >> shift) & 255;
+                }
+                // one atomic per distinct bin of the warp
+                const unsigned peers = __match_any_sync(0xffffffffu, bin);
+                if (bin >= 0 && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist_i[bin], __popc(peers));
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int cum = 0, sel = 0;
+                for (int b = 255; b >= 0; --b) {
+                    if (cum + hist_i[b] >= remaining) { sel = b; break; }
+                    cum += hist_i[b];
+                }
+                sh_prefix = prefix | ((uint32_t)sel << shift);
+                sh_remaining = (double)(remaining - cum);
+            }
+            __syncthreads();
+            prefix = sh_prefix;
+            remaining = (int)sh_remaining;
+            mask |= 255u << shift;
+            __syncthreads();
+        }
+        kth_key = prefix;
+    }
+
+    // ---- top-p: probability bits of the token where the descending mass reaches top_p * kept mass ----
+    uint32_t cut_bits = 0;  // keep everything (probabilities are >= 0, their bits order like the values)
+    if (top_p < 1.f) {
+        double mass = 0.0;
+        for (int i = tid; i < V; i += blockDim.x) {
+            const float l = penalised(lg, cnt, penalty, i);
+            if (order_key(l) >= kth_key) mass += (double)expf((l - mx) / temperature);
+        }
+        mass = block_sum_f64(mass, red_d);
+        uint32_t prefix = 0, mask = 0;
+        double remaining = (double)top_p * mass;
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            if (tid < 256) hist_d[tid] = 0.0;
+            __syncthreads();
+            for (int i = tid; i < V; i += blockDim.x) {
+                const float l = penalised(lg, cnt, penalty, i);
+                if (order_key(l) < kth_key) continue;
+                const float p = expf((l - mx) / temperature);
+                const uint32_t bits = __float_as_uint(p);
+                if ((bits & mask) == prefix) atomicAdd(&hist_d[(bits >> shift) & 255], (double)p);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                double cum = 0.0;
+                int sel = -1, lowest = 0;
+                for (int b = 255; b >= 0; --b) {
+                    if (hist_d[b] > 0.0) lowest = b;
+                    if (cum + hist_d[b] >= remaining && hist_d[b] > 0.0) { sel = b; break; }
+                    cum += hist_d[b];
+                }
+                if (sel < 0) {                    // rounding left the target just above the total
+                    sel = lowest;
+                    cum -= hist_d[lowest];
+                }
+                sh_prefix = prefix | ((uint32_t)sel << shift);
+                sh_remaining = remaining - cum;
+            }
+            __syncthreads();
+            prefix = sh_prefix;
+            remaining = sh_remaining;
+            mask |= 255u << shift;
+            __syncthreads();
+        }
+        cut_bits = prefix;
+    }
+
+    // ---- the draw: walk the kept tokens in token-id order ----
+    const int seg = (V + blockDim.x - 1) / blockDim.x;
+    const int s0 = min(V, tid * seg), s1 = min(V, s0 + seg);
+    double mine = 0.0;
+    for (int i = s0; i < s1; ++i) {
+        const float l = penalised(lg, cnt, penalty, i);
+        if (order_key(l) < kth_key) continue;
+        const float p = expf((l - mx) / temperature);
+        if (__float_as_uint(p) >= cut_bits) mine += (double)p;
+    }
+    seg_sum[tid] = mine;
+    __syncthreads();
+    if (tid == 0) {
+        double total = 0.0;
+        for (int t = 0; t < (int)blockDim.x; ++t) total += seg_sum[t];
+        const double target = (double)uniforms[row] * total;
+        double cum = 0.0;
+        int owner = -1;
+        for (int t = 0; t < (int)blockDim.x; ++t) {
+            if (cum + seg_sum[t] > target && seg_sum[t] > 0.0) { owner = t; break; }
+            cum += seg_sum[t];
+        }
+        if (owner < 0) {                         // rounding: take the last segment that holds mass
+            for (int t = (int)blockDim.x - 1; t >= 0; --t)
+                if (seg_sum[t] > 0.0) { owner = t; break; }
+            cum = -1.0;                           // marks "take the segment's last kept token"
+        }
+        sh_token = owner;
+        sh_remaining = cum;
+        red_d[0] = target;
+    }
+    __syncthreads();
+    if (tid == sh_token) {
+        const double target = red_d[0];
+        double cum = sh_remaining;
+        const bool take_last = cum < 0.0;
+        int tok = -1, last = -1;
+        for (int i = s0; i < s1; ++i) {
+            const float l = penalised(lg, cnt, penalty, i);
+            if (order_key(l) < kth_key) continue;
+            const float p = expf((l - mx) / temperature);
+            if (__float_as_uint(p) < cut_bits) continue;
+            last = i;
+            if (!take_last) {
+                cum += (double)p;
+                if (cum > target) { tok = i; break; }
+            }
+        }
+        if (tok < 0) tok = last;
+        out[row] = tok;
+        if (cnt) cnt[tok] += 1;
+    }
+}
+
+// counts: int32 [rows, V] occurrence counts of generated tokens (or null);
+// the sampled token's count is incremented.  uniforms: float [rows] in [0, 1)
+// (unused when temperature <= 0).
+TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float temperature, int top_k, float top_p,
+                     const float* uniforms, int* counts, float penalty, int* out, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (V <= 0 || ld < V) return (int)cudaErrorInvalidValue;
+    if (temperature > 0.f && !uniforms) return (int)cudaErrorInvalidValue;
+    if (counts && !(penalty > 0.f)) return (int)cudaErrorInvalidValue;
+    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, uniforms, counts,
+                                                         penalty, out);
+    return tq_launch_status();
+}

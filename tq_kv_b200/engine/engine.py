@@ -1,0 +1,165 @@
+"""The engine: a model, its cache and the one step function.
+
+`Engine.step(rows)` runs the tokens each row brings — whole prompts of unequal
+length in one step, or one token per sequence — as one packed batch from the
+cache and returns float32 logits at the wanted places.  Generation
+(`Engine.generate`, generate.py) and trace replay (replay.py) are loops above
+this one function.
+
+Reference: src/engine.rs:231-319 (load), :365-370 and :395-400 (the two
+forward calls per request that `step` generalises), :322-324 (clear_cache).
+There is no CPU path: the device must be a CUDA device.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from ..cache import PAGE_TOKENS, CacheError, SequenceCache
+from ..config import read_config_json, spec_from_config_dict
+from ..parts import Runtime
+from ..weights import load_tensors, random_tensors
+from ..weights.random_init import storage_dtype
+from .batch import StepRow, build_step_batch
+from .model import DecoderModel
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class StepError(ValueError):
+    """A step that cannot run; raised before anything is launched."""
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, config, config_dict: dict, runtime: Runtime, cache: SequenceCache):
+        self.model = model
+        self.config = config
+        self.config_dict = config_dict
+        self.runtime = runtime
+        self.cache = cache
+        self.spec = model.spec
+        self.vocab_size = model.spec.vocab_size
+        self.steps_run = 0
+
+    # ---- construction -------------------------------------------------------
+    @classmethod
+    def _build(cls, config_dict: dict, tensors_for, *, dtype, device, max_tokens: Optional[int],
+               max_slots: Optional[int], max_context: Optional[int]) -> "Engine":
+        if dtype not in _DTYPES:
+            raise ValueError(f"dtype must be 'bfloat16' or 'float32', not {dtype!r}")
+        mode = _DTYPES[dtype]
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError("this engine runs on a CUDA device only (there is no CPU path)")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is available; the engine cannot run")
+        arch, cfg, spec = spec_from_config_dict(config_dict)
+        model = DecoderModel(spec)
+        # cache geometry: context limit, then tokens held together, then slots
+        if max_context is None:
+            max_context = spec.max_positions if max_tokens is None else min(spec.max_positions,
+                                                                            _round_up(max_tokens, PAGE_TOKENS))
+        if max_context > spec.max_positions:
+            raise ValueError(f"max_context {max_context} exceeds the model's max positions {spec.max_positions}")
+        if max_tokens is None:
+            max_tokens = (max_slots or 1) * _round_up(max_context, PAGE_TOKENS)
+        if max_slots is None:
+            max_slots = max(1, -(-max_tokens // PAGE_TOKENS))
+        runtime = Runtime(device=dev, act_dtype=mode, max_context=max_context,
+                          sm_count=torch.cuda.get_device_properties(dev).multi_processor_count)
+        with torch.cuda.device(dev):
+            model.bind(tensors_for(model, mode, dev), runtime)
+            kv_req, state_req = model.cache_requests()
+            cache = SequenceCache(kv_req, state_req, max_tokens=max_tokens, max_slots=max_slots,
+                                  max_length=max_context, dtype=mode, device=dev)
+        return cls(model, cfg, config_dict, runtime, cache)
+
+    @classmethod
+    def from_folder(cls, folder: str, *, dtype="bfloat16", device="cuda:0", max_tokens: Optional[int] = None,
+                    max_slots: Optional[int] = None, max_context: Optional[int] = None) -> "Engine":
+        """Loads config.json and the safetensors files of `folder`."""
+        config_dict = read_config_json(folder)
+
+        def tensors_for(model: DecoderModel, mode, dev):
+            expected = {n: tuple(ws.shape) for n, ws in model.weight_specs().items()}
+            return load_tensors(folder, expected, model.ignored_weights(), mode=mode, device=dev)
+
+        return cls._build(config_dict, tensors_for, dtype=dtype, device=device, max_tokens=max_tokens,
+                          max_slots=max_slots, max_context=max_context)
+
+    @classmethod
+    def from_random(cls, config_dict: dict, seed: int = 0, *, dtype="bfloat16", device="cuda:0",
+                    max_tokens: Optional[int] = None, max_slots: Optional[int] = None,
+                    max_context: Optional[int] = None) -> "Engine":
+        """Random weights generated on the device (same rules as the folder
+        written by `write_model_folder`, without the trip through a file)."""
+        def tensors_for(model: DecoderModel, mode, dev):
+            stored = storage_dtype(config_dict.get("torch_dtype", "bfloat16"))
+            from ..weights.loader import target_dtype
+            out = {}
+            for name, t in random_tensors(model.weight_specs().values(), seed, stored, dev):
+                out[name] = t.to(target_dtype(t.dtype, mode))
+            return out
+
+        return cls._build(config_dict, tensors_for, dtype=dtype, device=device, max_tokens=max_tokens,
+                          max_slots=max_slots, max_context=max_context)
+
+    # ---- sequences ----------------------------------------------------------
+    def new_sequence(self) -> int:
+        """A free slot, length 0."""
+        return self.cache.alloc_slot()
+
+    def release(self, slot: int) -> None:
+        """Gives a slot and everything it holds back."""
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step -----------------------------------------------------------
+    def step(self, rows: Sequence[StepRow]) -> Optional[torch.Tensor]:
+        """Runs one step.  Every row brings >= 1 token; its tokens follow what
+        the row's slot already holds.  Returns float32 logits [wanted, vocab]
+        on the device, in the order of the rows and of each row's `want`
+        (None if nothing is wanted).  Nothing is changed if the step is
+        refused."""
+        rows = list(rows)
+        if not rows:
+            raise StepError("a step needs at least one row")
+        V = self.vocab_size
+        for r in rows:
+            if not r.tokens:
+                raise StepError(f"slot {r.slot}: Empty prompt")          # src/engine.rs:347-349
+            bad = [t for t in r.tokens if not 0 <= int(t) < V]
+            if bad:
+                raise StepError(f"slot {r.slot}: token id {bad[0]} is outside the vocabulary (0..{V - 1})")
+            for w in r.want:
+                if not 0 <= w < len(r.tokens):
+                    raise StepError(f"slot {r.slot}: wanted place {w} is outside the {len(r.tokens)} tokens brought")
+        slots = [r.slot for r in rows]
+        lens = [len(r.tokens) for r in rows]
+        for s in slots:
+            if not self.cache.book.slots.is_held(s):
+                raise StepError(f"slot {s} is not held")
+        self.model.check_step([self.cache.length(s) for s in slots], lens)
+        try:
+            self.cache.reserve(slots, lens)
+        except CacheError as e:
+            raise StepError(str(e)) from e
+        with torch.cuda.device(self.runtime.device):
+            batch = build_step_batch(rows, self.cache, self.runtime.device)
+            logits = self.model.forward(batch, self.cache)
+        self.cache.commit(slots, lens)
+        self.steps_run += 1
+        return logits
+
+    # ---- generation (see generate.py) ----------------------------------------
+    def generate(self, prompts, params=None, **kwargs):
+        from .generate import generate
+        return generate(self, prompts, params, **kwargs)

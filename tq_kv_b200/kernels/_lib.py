@@ -1,0 +1,83 @@
+"""ctypes bindings of the CUDA libraries: argument types, pointer and stream
+helpers, the error check.  No kernel has a CPU fallback: a tensor that is not
+on a CUDA device is an error, and so is a library that cannot be built."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_size_t, c_void_p
+
+import torch
+
+from ..csrc import build as _build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {t.dtype}")
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernels run on CUDA tensors only (this package has no CPU path)")
+    return t.data_ptr()
+
+
+def need_contiguous(**tensors: torch.Tensor | None) -> None:
+    for name, t in tensors.items():
+        if t is not None and not t.is_contiguous():
+            raise KernelError(f"'{name}' must be contiguous (shape {tuple(t.shape)}, strides {t.stride()})")
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise KernelError(f"{what}: CUDA error {status}" + (" (invalid argument)" if status == 1 else ""))
+
+
+_SIGNATURES = {
+    "tq_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tq_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+    "tq_qkv_rope_cache": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                          c_int, c_int, c_int, c_int, c_void_p],
+    "tq_swiglu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "tq_add_into": [c_void_p, c_void_p, c_int, c_size_t, c_void_p],
+    "tq_attention": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                     c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_gemm_tiled": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_int, c_void_p],
+    "tq_gemv_rows": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_int, c_int, c_int, c_void_p],
+    "tq_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p,
+                  c_void_p],
+}
+
+_core = None
+
+
+def core() -> ctypes.CDLL:
+    """The 'core' library, built at first use."""
+    global _core
+    if _core is None:
+        lib = _build.load("core")
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _core = lib
+    return _core

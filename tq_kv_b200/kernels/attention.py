@@ -1,0 +1,86 @@
+"""Python entry point of the attention kernel (csrc/attention.cu)."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream
+
+MAX_HEAD_DIM = 256
+
+
+def check_head_geometry(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+    """Raises for head sizes the attention kernels do not take."""
+    if head_dim % 16 or not 16 <= head_dim <= MAX_HEAD_DIM:
+        raise KernelError(f"attention: head_dim {head_dim} must be a multiple of 16 between 16 and {MAX_HEAD_DIM}")
+    if n_kv_heads <= 0 or n_heads % n_kv_heads:
+        raise KernelError(f"attention: {n_heads} heads cannot be shared among {n_kv_heads} key/value heads")
+    if n_kv_heads > 65535:
+        raise KernelError(f"attention: more than 65535 key/value heads ({n_kv_heads})")
+
+
+def plan_splits(n_tokens: int, n_kv_heads: int, max_keys: int, sm_count: int = 148) -> tuple[int, int]:
+    """(n_splits, split_len) for a step: one split while the grid fills the
+    GPU or the key ranges are short, else enough splits of a multiple of 32
+    keys to give every SM a few blocks."""
+    blocks = n_tokens * n_kv_heads
+    if blocks >= 2 * sm_count or max_keys <= 512:
+        return 1, 0
+    want = min(-(-4 * sm_count // blocks), -(-max_keys // 256), 64)
+    if want <= 1:
+        return 1, 0
+    split_len = -(-max_keys // want)
+    split_len = -(-split_len // 32) * 32
+    n_splits = -(-max_keys // split_len)
+    return (n_splits, split_len) if n_splits > 1 else (1, 0)
+
+
+def split_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return n_tokens * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
+              tok_pos: torch.Tensor, tok_seq: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
+              window: Optional[int], scale: Optional[float] = None,
+              k_packed: Optional[torch.Tensor] = None, v_packed: Optional[torch.Tensor] = None,
+              k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+              block_table: Optional[torch.Tensor] = None, table_width: int = 0, ring_pages: int = 0,
+              page_tokens: int = 64, n_splits: int = 1, split_len: int = 0,
+              scratch: Optional[torch.Tensor] = None):
+    """out[t, h] = softmax(q[t, h] · K / sqrt(head_dim)) · V over the keys
+    max(0, pos-window+1) .. pos of the token's sequence.  q/out [T, nh*hd].
+    Keys and values come from the step's packed rows (k_packed/v_packed
+    [T, nkv*hd]; every sequence must then start at position 0 or carry its
+    whole history in the step) or from the paged cache."""
+    check_head_geometry(n_heads, n_kv_heads, head_dim)
+    T = q.shape[0]
+    if q.shape[1] != n_heads * head_dim or out.shape != q.shape or out.dtype != q.dtype:
+        raise KernelError("attention: q and out must be [T, n_heads*head_dim] of one dtype")
+    packed = k_packed is not None
+    if packed:
+        if v_packed is None or k_packed.dtype != q.dtype or k_packed.shape != (T, n_kv_heads * head_dim):
+            raise KernelError("attention: packed keys/values must be [T, n_kv_heads*head_dim] of q's dtype")
+    else:
+        if k_pages is None or v_pages is None or block_table is None or k_pages.dtype != q.dtype:
+            raise KernelError("attention: no key/value source of q's dtype was given")
+        if tuple(k_pages.shape[1:]) != (n_kv_heads, page_tokens, head_dim):
+            raise KernelError(f"attention: cache pages have shape {tuple(k_pages.shape)}")
+    part_acc = part_ml = None
+    if n_splits > 1:
+        need = split_scratch_floats(T, n_heads, head_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention: {n_splits} splits need {need} float32 of scratch")
+        n_acc = T * n_heads * n_splits * head_dim
+        part_acc, part_ml = scratch[:n_acc], scratch[n_acc:need]
+    need_contiguous(q=q, out=out, k_packed=k_packed, v_packed=v_packed, k_pages=k_pages, v_pages=v_pages,
+                    block_table=block_table)
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    check(core().tq_attention(
+        ptr(q), dtype_code(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table),
+        table_width, ring_pages, page_tokens, ptr(tok_pos), ptr(tok_seq), ptr(cu_seqlens), ptr(start_pos),
+        int(window or 0), float(scale), ptr(out), ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, head_dim,
+        n_splits, split_len, stream()), "attention")
+    return out

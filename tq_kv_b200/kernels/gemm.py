@@ -1,0 +1,90 @@
+"""Matrix products: y = x · W^T with W stored [out, in].
+
+`linear()` picks the kernel from the operands:
+  * few rows (decoding): the hand-written row kernel of csrc/gemm.cu, which
+    streams the weight once per 8 rows and fuses bias, SwiGLU gating and the
+    float32 accumulation into the residual stream;
+  * many rows, bfloat16 × bfloat16: the library matrix product (cuBLAS through
+    torch.mm with float32 output), as the reference engine does for all its
+    products (src/models/turbo_generic.rs:68-91 -> candle -> cuBLAS);
+  * everything else (the float32 path, mixed operands): the tiled float32
+    FMA kernel of csrc/gemm.cu — never a reduced-precision mode.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import elementwise
+from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream
+
+ROW_KERNEL_MAX_ROWS = 16
+
+
+def gemm_tiled(x, w, out, bias=None, accumulate=False):
+    M, K = x.shape
+    N = w.shape[0]
+    check(core().tq_gemm_tiled(ptr(x), dtype_code(x), ptr(w), dtype_code(w), ptr(bias), ptr(out), dtype_code(out),
+                               M, N, K, x.stride(0), w.stride(0), out.stride(0), int(accumulate), stream()),
+          "gemm_tiled")
+    return out
+
+
+def gemv_rows(x, w, out, bias=None, accumulate=False, swiglu=False):
+    M, K = x.shape
+    N = out.shape[1]
+    check(core().tq_gemv_rows(ptr(x), dtype_code(x), ptr(w), dtype_code(w), ptr(bias), ptr(out), dtype_code(out),
+                              M, N, K, x.stride(0), w.stride(0), out.stride(0), int(accumulate), int(swiglu),
+                              stream()), "gemv_rows")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+           accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+    """y = x · w^T (+ bias); with `swiglu`, w holds gate rows then up rows and
+    y = silu(x · gate^T) * (x · up^T); with `accumulate`, `out` (float32) gets
+    y added to it.  x [M, K], w [N, K] (or [2N, K]); float32 accumulation
+    throughout."""
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise KernelError(f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not multiply")
+    if x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("linear: operands must be contiguous along the inner dimension")
+    M, K = x.shape
+    rows_w = w.shape[0]
+    if swiglu and rows_w % 2:
+        raise KernelError("linear: a SwiGLU weight needs an even number of rows")
+    N = rows_w // 2 if swiglu else rows_w
+    if accumulate:
+        if out is None or out.dtype != torch.float32:
+            raise KernelError("linear: accumulate needs a float32 `out`")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    if tuple(out.shape) != (M, N) or out.stride(1) != 1:
+        raise KernelError(f"linear: out has shape {tuple(out.shape)}, expected {(M, N)}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != rows_w):
+        raise KernelError("linear: bias must be float32 with one entry per weight row")
+    if M == 0:
+        return out
+
+    if M <= ROW_KERNEL_MAX_ROWS:
+        return gemv_rows(x, w, out, bias, accumulate, swiglu)
+
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and bias is None:
+        y = torch.mm(x, w.t(), out_dtype=torch.float32)          # library product, float32 out
+        if swiglu:
+            return elementwise.swiglu(y, out)
+        if accumulate:
+            return elementwise.add_into(out, y)
+        if out.dtype == torch.float32:
+            out.copy_(y)
+        else:
+            out.copy_(y)
+        return out
+
+    if swiglu:
+        y = torch.empty((M, rows_w), dtype=torch.float32, device=x.device)
+        gemm_tiled(x, w, y, bias, False)
+        return elementwise.swiglu(y, out)
+    return gemm_tiled(x, w, out, bias, accumulate)
