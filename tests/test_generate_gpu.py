@@ -1,0 +1,99 @@
+"""Generation through the Python entry point and the command line against the
+plain implementation's generation (GPU)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_model as pm
+from helpers import TINY, model_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+
+
+@pytest.fixture(scope="module")
+def tmp_root(tmp_path_factory):
+    return tmp_path_factory.mktemp("gen")
+
+
+def test_greedy_generation_through_the_entry_point(tmp_root):
+    """BASELINE workload of tiny A: prompts of 5/9/13 tokens, 8 greedy steps."""
+    import tq_kv_b200 as tq
+    folder = model_folder(tmp_root, "a", "float32")
+    cfg, w = pm.read_model_folder(folder)
+    prompts = [random_tokens(n, 256, 60 + n) for n in (5, 9, 13)]
+    eng = tq.load(folder, dtype="float32", max_batch=3, max_context=64)
+    res = eng.generate(prompts, tq.GenerationParams.greedy(8, stop_token_ids=()))
+    for p, r in zip(prompts, res):
+        assert r.tokens == pm.generate(cfg, w, p, 8) and r.finish_reason == "length"
+    assert eng.cache.free_slots == 3
+    eng.cache.book.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling_with_fixed_seed(tmp_root, dtype):
+    """BASELINE workload of tiny B: prompts of 1/7/20/33 tokens, 12 steps at
+    temperature 0.8; the plain sampler gets the same uniform draws.  Then the
+    reference's defaults (top-k 40, top-p 0.9, repeat penalty 1.1), more
+    requests than slots, and a stop token."""
+    import tq_kv_b200 as tq
+    from tq_kv_b200.sampling import uniform
+    folder = model_folder(tmp_root, "b", "float32")
+    cfg, w = pm.read_model_folder(folder)
+    prompts = [random_tokens(n, 1000, 70 + n) for n in (1, 7, 20, 33)]
+    eng = tq.load(folder, dtype=dtype, max_batch=2, max_context=128)
+    f32 = lambda x: float(torch.tensor(x, dtype=torch.float32))
+    for params in (tq.GenerationParams(max_tokens=12, temperature=0.8, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=5,
+                                       stop_token_ids=()),
+                   tq.GenerationParams(max_tokens=12, seed=9, stop_token_ids=())):
+        res = eng.generate(prompts, params)
+        agree = 0
+        for i, (p, r) in enumerate(zip(prompts, res)):
+            us = [uniform(params.seed, i, k) for k in range(12)]
+            want = pm.generate(cfg, w, p, 12, temperature=f32(params.temperature), top_k=params.top_k,
+                               top_p=f32(params.top_p), repeat_penalty=f32(params.repeat_penalty), uniforms=us)
+            if dtype == "float32":
+                assert r.tokens == want, (i, params)
+            agree += sum(a == b for a, b in zip(r.tokens, want))
+            assert len(r.tokens) == 12
+        assert agree >= 40 or dtype == "float32"      # bfloat16 logits may flip a draw that sits on an edge
+    # a stop token ends a request early without being emitted
+    free = eng.generate(prompts[:2], tq.GenerationParams.greedy(6, stop_token_ids=()))
+    stop = free[1].tokens[-1]
+    res = eng.generate(prompts[:2], tq.GenerationParams.greedy(6, stop_token_ids=(stop,)))
+    for f, r in zip(free, res):
+        if stop in f.tokens:
+            assert r.tokens == f.tokens[:f.tokens.index(stop)] and r.finish_reason == "stop"
+        else:
+            assert r.tokens == f.tokens and r.finish_reason == "length"
+    assert eng.cache.free_slots == 2 and eng.cache.free_pages() == 4
+
+
+def test_command_line_run_bench_and_perplexity(tmp_root):
+    import tq_kv_b200 as tq
+    from tq_kv_b200.cli import perplexity
+    folder = model_folder(tmp_root, "b", "float32")
+    cfg, w = pm.read_model_folder(folder)
+    env = {**os.environ, "PYTHONPATH": ROOT}
+    tq_bin = os.path.join(ROOT, "bin", "tq")
+    out = subprocess.run([sys.executable, tq_bin, "run", folder, "--dtype", "float32", "-n", "5", "-t", "0",
+                          "--prompt-ids", "5,6,7", "--prompt-ids", "9"], capture_output=True, text=True, env=env)
+    assert out.returncode == 0, out.stderr
+    lines = [[int(t) for t in l.split(",")] for l in out.stdout.strip().splitlines()]
+    # -t 0 is arg-max; top-k/top-p do not matter then, the default repeat penalty 1.1 does
+    assert lines == [pm.generate(cfg, w, p, 5, repeat_penalty=float(torch.tensor(1.1, dtype=torch.float32)))
+                     for p in ([5, 6, 7], [9])]
+    out = subprocess.run([sys.executable, tq_bin, "bench", folder, "--dtype", "float32", "-n", "8", "--json",
+                          "--prompt-ids", "1,2,3,4"], capture_output=True, text=True, env=env)
+    assert out.returncode == 0, out.stderr
+    rec = json.loads(out.stdout.strip().splitlines()[-1])
+    assert rec["tokens"] == 8 and rec["tok_per_sec"] > 0 and rec["ttft_secs"] > 0
+    toks = random_tokens(30, 1000, 3)
+    eng = tq.load(folder, dtype="float32", max_batch=1, max_context=64)
+    logp = torch.log_softmax(pm.decoder_logits(cfg, w, toks).double(), -1)
+    nll = -sum(float(logp[t, toks[t + 1]]) for t in range(29)) / 29
+    assert abs(perplexity(eng, toks) - float(torch.exp(torch.tensor(nll)))) < 1e-2

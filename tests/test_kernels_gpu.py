@@ -1,0 +1,397 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch computation of the
+same operation, at sizes other than the tiny models' (GPU)."""
+import math
+
+import pytest
+import torch
+
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, want, tol, what=""):
+    got, want = got.float().cpu(), want.float().cpu()
+    assert torch.isfinite(got).all(), what
+    err = float((got - want).abs().max())
+    assert err <= tol * max(1.0, float(want.abs().max())), f"{what}: {err:.3e}"
+
+
+# ---- embedding, norm, gating --------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    from tq_kv_b200 import kernels
+    table = rnd(1000, 200, dtype=dtype)
+    toks = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 200, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.embed(toks, table, out, status)
+    assert torch.equal(out, table[toks.long()].float()) and int(status) == 0
+    kernels.embed(torch.tensor([3, 1000], dtype=torch.int32, device=DEV), table, out[:2], status)
+    assert int(status) == 1 and float(out[1].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("H,out_dtype", [(1000, torch.float32), (72, torch.bfloat16), (3584, torch.bfloat16)])
+def test_rmsnorm(H, out_dtype):
+    from tq_kv_b200 import kernels
+    x, w = rnd(7, H, scale=3.0), rnd(H) + 1.0
+    out = torch.empty(7, H, dtype=out_dtype, device=DEV)
+    kernels.rmsnorm(x, w, 1e-5, out)
+    want = pm.rms_norm(x.cpu(), w.cpu(), 1e-5)
+    close(out, want, 1e-6 if out_dtype == torch.float32 else 4e-3, "rmsnorm")
+    rows = torch.tensor([6, 0, 6], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, H, dtype=out_dtype, device=DEV)
+    kernels.rmsnorm(x, w, 1e-5, out, rows)
+    close(out, want[[6, 0, 6]], 1e-6 if out_dtype == torch.float32 else 4e-3, "rmsnorm rows")
+
+
+def test_swiglu_and_add_into():
+    from tq_kv_b200 import kernels
+    gu = rnd(5, 2 * 203, scale=2.0)
+    out = torch.empty(5, 203, dtype=torch.bfloat16, device=DEV)
+    kernels.swiglu(gu, out)
+    want = torch.nn.functional.silu(gu[:, :203]) * gu[:, 203:]
+    close(out, want, 4e-3, "swiglu")
+    acc, x = rnd(9, 77), rnd(9, 77, dtype=torch.bfloat16, seed=1)
+    want = acc + x.float()
+    kernels.add_into(acc, x)
+    assert torch.equal(acc, want)
+
+
+# ---- matrix products ------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(70, 130, 50), (1, 64, 16), (129, 65, 203)])
+@pytest.mark.parametrize("dts", [(torch.float32,) * 3, (torch.bfloat16, torch.bfloat16, torch.float32),
+                                 (torch.bfloat16, torch.float32, torch.bfloat16)])
+def test_gemm_tiled(M, N, K, dts):
+    from tq_kv_b200 import kernels
+    a, w, bias = rnd(M, K, dtype=dts[0]), rnd(N, K, dtype=dts[1], seed=1), rnd(N, seed=2)
+    out = torch.empty(M, N, dtype=dts[2], device=DEV)
+    kernels.gemm_tiled(a, w, out, bias)
+    want = a.double() @ w.double().T + bias.double()
+    tol = 2e-6 if dts[2] == torch.float32 else 4e-3
+    close(out, want, tol, "gemm_tiled")
+    if dts[2] == torch.float32:
+        kernels.gemm_tiled(a, w, out, None, accumulate=True)
+        close(out, 2 * want - bias.double(), tol, "gemm_tiled accumulate")
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 11, 16])
+@pytest.mark.parametrize("K,dt", [(200, torch.bfloat16), (203, torch.bfloat16), (100, torch.float32),
+                                  (3584, torch.bfloat16)])
+def test_gemv_rows(M, K, dt):
+    from tq_kv_b200 import kernels
+    N = 37
+    a, w, bias = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, seed=1), rnd(N, seed=2)
+    out = rnd(M, N, seed=3)
+    base = out.clone()
+    kernels.gemv_rows(a, w, out, bias, accumulate=True)
+    want = base.double() + a.double() @ w.double().T + bias.double()
+    close(out, want, 3e-6 * math.sqrt(K / 100), "gemv accumulate")
+    w2 = rnd(2 * N, K, dtype=dt, seed=4, scale=0.2)
+    out = torch.empty(M, N, dtype=dt, device=DEV)
+    kernels.gemv_rows(a, w2, out, swiglu=True)
+    y = a.double() @ w2.double().T
+    want = torch.nn.functional.silu(y[:, :N]) * y[:, N:]
+    close(out, want, 1e-5 if dt == torch.float32 else 4e-3, "gemv swiglu")
+
+
+@pytest.mark.parametrize("M", [5, 16, 17, 300])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_linear_picks_a_kernel_for_every_shape(M, dt):
+    from tq_kv_b200 import kernels
+    K, N = 136, 210
+    x, w = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, seed=1, scale=0.1)
+    want = x.double() @ w.double().T
+    close(kernels.linear(x, w, out_dtype=torch.float32), want, 5e-6, "linear")
+    res = rnd(M, N, seed=5)
+    want_acc = res.double() + want
+    kernels.linear(x, w, out=res, accumulate=True)
+    close(res, want_acc, 5e-6, "linear accumulate")
+    w2 = rnd(2 * N, K, dtype=dt, seed=2, scale=0.1)
+    y = x.double() @ w2.double().T
+    close(kernels.linear(x, w2, swiglu=True, out_dtype=dt), torch.nn.functional.silu(y[:, :N]) * y[:, N:],
+          1e-5 if dt == torch.float32 else 4e-3, "linear swiglu")
+    if dt == torch.bfloat16:        # a 32-bit weight under 16-bit activations stays 32-bit
+        wf = rnd(N, K, seed=3, scale=0.1)
+        close(kernels.linear(x, wf, out_dtype=torch.float32), x.double() @ wf.double().T, 5e-6, "mixed")
+
+
+# ---- rotary encoding and cache append ----------------------------------------------
+@pytest.mark.parametrize("cache_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 5, 48, 48), (6, 2, 80, 32), (3, 1, 16, 16)])
+def test_qkv_rope_cache(cache_dtype, nh, nkv, hd, rot):
+    from tq_kv_b200 import kernels
+    lens, starts = [70, 3, 1], [0, 130, 64]            # row 0: a prompt; rows 1, 2: continuations
+    T, B = sum(lens), 3
+    width = (nh + 2 * nkv) * hd
+    qkv, bias = rnd(T, width), rnd(width, seed=1)
+    cos, sin = pm.rope_tables(rot, 50000.0, 256)
+    tok_seq = torch.tensor(sum(([b] * n for b, n in enumerate(lens)), []), dtype=torch.int32, device=DEV)
+    pos = sum((list(range(s, s + n)) for s, n in zip(starts, lens)), [])
+    tok_pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    new_lens = torch.tensor([s + n for s, n in zip(starts, lens)], dtype=torch.int32, device=DEV)
+    pages, P = 9, 64
+    table = torch.tensor([[4, 7, 0], [1, 8, 2], [3, 5, 6]], dtype=torch.int32, device=DEV)
+    kp = torch.zeros(pages, nkv, P, hd, dtype=cache_dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    q = torch.empty(T, nh * hd, dtype=cache_dtype, device=DEV)
+    k = torch.empty(T, nkv * hd, dtype=cache_dtype, device=DEV)
+    v = torch.empty_like(k)
+    kernels.qkv_rope_cache(qkv, bias, cos.to(DEV), sin.to(DEV), tok_pos, tok_seq, new_lens, q, n_heads=nh,
+                           n_kv_heads=nkv, head_dim=hd, rotary_dim=rot, k_out=k, v_out=v, k_pages=kp, v_pages=vp,
+                           block_table=table, table_width=3, ring_pages=0, page_tokens=P)
+    x = (qkv + bias).cpu()
+    xq = x[:, :nh * hd].reshape(T, nh, hd)
+    xk = x[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd)
+    xv = x[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+
+    def rope(t):       # [T, heads, hd] with each token at its own position
+        r = torch.stack([pm.rope_halved(t[i:i + 1, :, :rot].transpose(0, 1), cos[p:p + 1], sin[p:p + 1])[:, 0]
+                         for i, p in enumerate(pos)])
+        return torch.cat([r, t[:, :, rot:]], dim=-1)
+
+    tol = 1e-6 if cache_dtype == torch.float32 else 4e-3
+    wq, wk = rope(xq), rope(xk)
+    close(q, wq.reshape(T, -1), tol, "q")
+    close(k, wk.reshape(T, -1), tol, "k packed")
+    close(v, xv.reshape(T, -1), tol, "v packed")
+    tbl = table.cpu()
+    for i, (b, p) in enumerate(zip(tok_seq.tolist(), pos)):
+        page = int(tbl[b, p // P])
+        close(kp[page, :, p % P], wk[i], tol, "k cache")
+        close(vp[page, :, p % P], xv[i], tol, "v cache")
+    written = sum(lens) * nkv * hd
+    assert int((vp != 0).sum()) == written               # nothing else was touched
+
+
+def test_ring_keeps_only_the_last_positions_of_a_long_prompt():
+    from tq_kv_b200 import kernels
+    nh = nkv = 1
+    hd, P, ring = 16, 64, 2
+    n = 300                                              # 300 tokens onto a ring of 128
+    qkv = rnd(n, 3 * hd)
+    cos, sin = pm.rope_tables(hd, 1e4, 512)
+    tok_pos = torch.arange(n, dtype=torch.int32, device=DEV)
+    tok_seq = torch.zeros(n, dtype=torch.int32, device=DEV)
+    new_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[2, 0]], dtype=torch.int32, device=DEV)
+    kp = torch.zeros(3, 1, P, hd, device=DEV)
+    vp = torch.zeros_like(kp)
+    q = torch.empty(n, hd, device=DEV)
+    kernels.qkv_rope_cache(qkv, None, cos.to(DEV), sin.to(DEV), tok_pos, tok_seq, new_lens, q, n_heads=1,
+                           n_kv_heads=1, head_dim=hd, rotary_dim=hd, k_pages=kp, v_pages=vp, block_table=table,
+                           table_width=2, ring_pages=ring, page_tokens=P)
+    for p in range(n - ring * P, n):
+        page = [2, 0][(p // P) % ring]
+        assert torch.equal(vp[page, 0, p % P], qkv[p, 2 * hd:]), p
+    assert float(vp[1].abs().sum()) == 0.0
+
+
+# ---- attention ----------------------------------------------------------------------
+def plain_attention(q, k, v, nh, nkv, hd, window, q_pos):
+    """q [Tq, nh*hd] at absolute positions q_pos over keys 0..Tk-1, float64."""
+    Tq, Tk = q.shape[0], k.shape[0]
+    q = q.double().reshape(Tq, nh, hd).transpose(0, 1)
+    k = pm.repeat_kv(k.double().reshape(Tk, nkv, hd).transpose(0, 1), nh // nkv)
+    v = pm.repeat_kv(v.double().reshape(Tk, nkv, hd).transpose(0, 1), nh // nkv)
+    att = q @ k.transpose(1, 2) / math.sqrt(hd)
+    i = torch.tensor(q_pos).reshape(-1, 1)
+    j = torch.arange(Tk).reshape(1, -1)
+    masked = j > i
+    if window:
+        masked = masked | (j < i - window + 1)
+    att = torch.where(masked.unsqueeze(0), torch.full_like(att, float("-inf")), att)
+    return (pm.softmax_last_dim(att) @ v).transpose(0, 1).reshape(Tq, nh * hd)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(7, 1, 128, None), (6, 3, 48, 20), (5, 5, 16, None), (16, 2, 256, 33),
+                                              (24, 2, 80, None)])
+def test_attention_over_packed_prompts(dtype, nh, nkv, hd, window):
+    from tq_kv_b200 import kernels
+    lens = [1, 37, 90]
+    T = sum(lens)
+    q, k, v = rnd(T, nh * hd, dtype=dtype), rnd(T, nkv * hd, dtype=dtype, seed=1), rnd(T, nkv * hd, dtype=dtype, seed=2)
+    cu = [0, 1, 38, 128]
+    tok_seq = torch.tensor(sum(([b] * n for b, n in enumerate(lens)), []), dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(sum((list(range(n)) for n in lens), []), dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    kernels.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd, tok_pos=tok_pos, tok_seq=tok_seq,
+                      cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                      start_pos=torch.zeros(3, dtype=torch.int32, device=DEV), window=window, k_packed=k, v_packed=v)
+    for b, n in enumerate(lens):
+        a, e = cu[b], cu[b + 1]
+        want = plain_attention(q[a:e].cpu(), k[a:e].cpu(), v[a:e].cpu(), nh, nkv, hd, window, list(range(n)))
+        close(out[a:e], want, 2e-6 if dtype == torch.float32 else 8e-3, f"row {b}")
+
+
+def _paged(k, v, nkv, hd, table_row, P=64):
+    """Scatters [Tk, nkv*hd] keys/values into pages per `table_row`."""
+    n_pages = max(table_row) + 2
+    kp = torch.full((n_pages, nkv, P, hd), 1e4, dtype=k.dtype, device=DEV)    # unwritten rows hold junk, not zeros
+    vp = torch.full_like(kp, 1e4)
+    for j in range(k.shape[0]):
+        kp[table_row[j // P], :, j % P] = k[j].reshape(nkv, hd)
+        vp[table_row[j // P], :, j % P] = v[j].reshape(nkv, hd)
+    return kp, vp
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window,n_splits", [(28, 4, 128, None, 1), (28, 4, 128, None, 5),
+                                                       (3, 1, 32, 100, 3), (6, 6, 48, None, 7)])
+def test_attention_over_the_paged_cache_with_splits(dtype, nh, nkv, hd, window, n_splits):
+    from tq_kv_b200 import kernels
+    Tk = 700
+    k, v = rnd(Tk, nkv * hd, dtype=dtype, seed=1), rnd(Tk, nkv * hd, dtype=dtype, seed=2)
+    table_row = [9, 3, 0, 11, 5, 7, 2, 10, 1, 6, 4]
+    kp, vp = _paged(k, v, nkv, hd, table_row)
+    q_pos = [699, 64, 0, 511]                          # four "sequences" sharing the pages, of different lengths
+    B = len(q_pos)
+    q = rnd(B, nh * hd, dtype=dtype)
+    table = torch.tensor([table_row] * B, dtype=torch.int32, device=DEV)
+    split_len = -(-(-(-700 // n_splits)) // 32) * 32 if n_splits > 1 else 0
+    scratch = torch.empty(kernels.split_scratch_floats(B, nh, hd, n_splits), device=DEV) if n_splits > 1 else None
+    out = torch.empty_like(q)
+    kernels.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                      tok_pos=torch.tensor(q_pos, dtype=torch.int32, device=DEV),
+                      tok_seq=torch.arange(B, dtype=torch.int32, device=DEV),
+                      cu_seqlens=torch.arange(B + 1, dtype=torch.int32, device=DEV),
+                      start_pos=torch.tensor(q_pos, dtype=torch.int32, device=DEV), window=window,
+                      k_pages=kp, v_pages=vp, block_table=table, table_width=len(table_row),
+                      n_splits=n_splits, split_len=split_len, scratch=scratch)
+    want = torch.cat([plain_attention(q[b:b + 1].cpu(), k[:p + 1].cpu(), v[:p + 1].cpu(), nh, nkv, hd, window, [p])
+                      for b, p in enumerate(q_pos)])
+    close(out, want, 2e-6 if dtype == torch.float32 else 8e-3, "paged")
+
+
+@pytest.mark.parametrize("n_splits", [1, 6])
+def test_a_far_key_among_hundreds_is_found(n_splits):
+    """Random scores are nearly flat, so a dropped key would hardly show.  Here
+    one key far back (position 3 of 700) matches the query strongly and its
+    value is distinct: the output must be that value."""
+    from tq_kv_b200 import kernels
+    nh, nkv, hd, Tk = 4, 2, 64, 700
+    k, v = rnd(Tk, nkv * hd, scale=0.1, seed=1), rnd(Tk, nkv * hd, scale=0.1, seed=2)
+    q = rnd(1, nh * hd, scale=0.1)
+    k[3] = 0
+    k[3, :hd] = 8.0
+    k[3, hd:] = 8.0
+    q[:] = 8.0
+    v[3] = 5.0
+    table_row = list(range(11))
+    kp, vp = _paged(k, v, nkv, hd, table_row)
+    split_len = 128 if n_splits > 1 else 0
+    scratch = torch.empty(kernels.split_scratch_floats(1, nh, hd, n_splits), device=DEV) if n_splits > 1 else None
+    out = torch.empty_like(q)
+    args = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, tok_pos=torch.tensor([699], dtype=torch.int32, device=DEV),
+                tok_seq=torch.zeros(1, dtype=torch.int32, device=DEV),
+                cu_seqlens=torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                start_pos=torch.tensor([699], dtype=torch.int32, device=DEV), k_pages=kp, v_pages=vp,
+                block_table=torch.tensor([table_row], dtype=torch.int32, device=DEV), table_width=11,
+                n_splits=n_splits, split_len=split_len, scratch=scratch)
+    kernels.attention(q, out, window=None, **args)
+    assert float((out - 5.0).abs().max()) < 1e-3
+    # the window's edge: with 697 keys in view key 3 is the oldest one seen, with 696 it is out
+    kernels.attention(q, out, window=697, **args)
+    assert float((out - 5.0).abs().max()) < 1e-3
+    kernels.attention(q, out, window=696, **args)
+    assert float(out.abs().max()) < 1.0
+
+
+def test_ring_cache_decoding_reads_the_right_rows():
+    """A window of 100 on a ring of 2 pages: position 300 sees 201..300, which
+    lie in ring rows (p % 128) of two physical pages."""
+    from tq_kv_b200 import kernels
+    nh, nkv, hd, W, P, ring = 2, 1, 32, 100, 64, 2
+    n = 301
+    k, v = rnd(n, hd, seed=1), rnd(n, hd, seed=2)
+    kp = torch.full((4, 1, P, hd), 1e4, device=DEV)
+    vp = torch.full_like(kp, 1e4)
+    phys = [3, 1]
+    for p in range(n - ring * P, n):
+        kp[phys[(p // P) % ring], 0, p % P] = k[p]
+        vp[phys[(p // P) % ring], 0, p % P] = v[p]
+    q = rnd(1, nh * hd)
+    out = torch.empty_like(q)
+    kernels.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                      tok_pos=torch.tensor([300], dtype=torch.int32, device=DEV),
+                      tok_seq=torch.zeros(1, dtype=torch.int32, device=DEV),
+                      cu_seqlens=torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                      start_pos=torch.tensor([300], dtype=torch.int32, device=DEV), window=W, k_pages=kp, v_pages=vp,
+                      block_table=torch.tensor([phys], dtype=torch.int32, device=DEV), table_width=2,
+                      ring_pages=ring)
+    want = plain_attention(q.cpu(), k.cpu(), v.cpu(), nh, nkv, hd, W, [300])
+    close(out, want, 2e-6, "ring")
+
+
+def test_sizes_outside_the_kernels_reach_are_refused():
+    from tq_kv_b200 import kernels
+    with pytest.raises(kernels.KernelError, match="head_dim"):
+        kernels.check_head_geometry(4, 2, 24)
+    with pytest.raises(kernels.KernelError, match="head_dim"):
+        kernels.check_head_geometry(4, 2, 272)
+    with pytest.raises(kernels.KernelError, match="shared"):
+        kernels.check_head_geometry(5, 2, 64)
+    with pytest.raises(kernels.KernelError, match="CUDA"):
+        kernels.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-6, torch.zeros(2, 8))
+
+
+# ---- sampling -----------------------------------------------------------------------
+@pytest.mark.parametrize("V", [1000, 50257])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.0, 0, 1.0), (0.8, 0, 1.0), (1.0, 40, 1.0), (0.7, 0, 0.9),
+                                                     (0.7, 40, 0.9), (1.5, 5, 0.5), (1.0, 1, 1.0)])
+def test_sample_follows_the_plain_sampler(V, temperature, top_k, top_p):
+    from tq_kv_b200 import kernels
+    R = 6
+    logits = rnd(R, V, scale=3.0, seed=V)
+    top_p32 = float(torch.tensor(top_p, dtype=torch.float32))
+    us = [0.0, 0.13, 0.5, 0.77, 0.999, 0.31]
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    kernels.sample(logits, out, temperature=temperature, top_k=top_k, top_p=top_p,
+                   uniforms=torch.tensor(us, device=DEV))
+    want = [pm.sample(logits[r].cpu(), temperature, top_k, top_p32, us[r]) for r in range(R)]
+    assert out.tolist() == want
+
+
+def test_argmax_ties_go_to_the_lowest_id():
+    from tq_kv_b200 import kernels
+    logits = torch.zeros(2, 5000, device=DEV)
+    logits[0, [4321, 77, 3000]] = 2.0
+    logits[1, 4999] = 1.0
+    out = torch.zeros(2, dtype=torch.int32, device=DEV)
+    kernels.sample(logits, out)
+    assert out.tolist() == [77, 4999]
+
+
+def test_repeat_penalty_counts_every_occurrence():
+    from tq_kv_b200 import kernels
+    V = 300
+    logits = rnd(2, V, scale=2.0, seed=3)
+    counts = torch.zeros(2, V, dtype=torch.int32, device=DEV)
+    hist = [[5, 9, 5, 200], [17]]
+    for r, h in enumerate(hist):
+        for t in h:
+            counts[r, t] += 1
+    before = counts.clone()
+    out = torch.zeros(2, dtype=torch.int32, device=DEV)
+    us = [0.4, 0.9]
+    kernels.sample(logits, out, temperature=0.9, top_k=50, top_p=0.95, uniforms=torch.tensor(us, device=DEV),
+                   counts=counts, repeat_penalty=1.3)
+    p95 = float(torch.tensor(0.95, dtype=torch.float32))
+    want = [pm.sample(pm.apply_repeat_penalty(logits[r].cpu(), hist[r], 1.3), 0.9, 50, p95, us[r]) for r in range(2)]
+    assert out.tolist() == want
+    before[0, want[0]] += 1
+    before[1, want[1]] += 1
+    assert torch.equal(counts, before)                   # the chosen tokens were counted
+    # greedy with a penalty strong enough to dethrone the best token
+    best = int(logits[0].argmax())
+    counts.zero_()
+    counts[0, best] = 3
+    kernels.sample(logits, out, counts=counts, repeat_penalty=50.0)
+    assert out.tolist()[0] == pm.greedy(pm.apply_repeat_penalty(logits[0].cpu(), [best] * 3, 50.0)) != best

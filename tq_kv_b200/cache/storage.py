@@ -146,5 +146,13 @@ class SequenceCache:
         g = self.groups[gi]
         return gi, g.k[li], g.v[li]
 
+    def free_pages(self) -> int:
+        """Pages a new sequence can still get: the scarcest all-keys group
+        decides (a window group never needs more pages than those)."""
+        full = [g.book.pool.free_count for g in self.groups if g.book.ring_pages is None]
+        if full:
+            return min(full)
+        return min((g.book.pool.free_count for g in self.groups), default=1 << 30)
+
     def bytes(self) -> int:
         return sum(g.bytes() for g in self.groups) + sum(t.numel() * t.element_size() for t in self.state.values())

@@ -58,6 +58,8 @@ def write_model_folder(config_dict: dict, folder: str, seed: int, *, device="cpu
     dtype = storage_dtype(config_dict.get("torch_dtype", "bfloat16"))
     os.makedirs(folder, exist_ok=True)
     full = cfg.to_dict() if hasattr(cfg, "to_dict") else dict(config_dict)
+    full["architectures"] = [arch.name]          # the name the registry resolved, not the config class's own
+    full["model_type"] = arch.model_type
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(full, f, indent=1)
     write_safetensors(os.path.join(folder, "model.safetensors"),
