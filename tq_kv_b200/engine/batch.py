@@ -79,4 +79,4 @@ def build_step_batch(rows: list[StepRow], cache: SequenceCache, device) -> StepB
         n_tokens=T, n_seqs=B, tokens=seg(0, T), tok_seq=seg(1, T), tok_pos=seg(2, T), cu_seqlens=seg(3, B + 1),
         slots=seg(4, B), start_pos=seg(5, B), new_lens=seg(6, B), logit_rows=seg(7, R), n_logit_rows=R,
         block_tables=[(seg(8 + gi, B * max(w, 1)), max(w, 1)) for gi, (_, w) in enumerate(tables)],
-        host_slots=slots, host_start=starts, host_lens=lens)
+        host_slots=slots, host_start=starts, host_lens=lens, packed_bytes=int(buf.nbytes))

@@ -46,6 +46,7 @@ class Engine:
         self.spec = model.spec
         self.vocab_size = model.spec.vocab_size
         self.steps_run = 0
+        self.h2d_bytes = 0            # bytes of step inputs copied to the device so far
 
     # ---- construction -------------------------------------------------------
     @classmethod
@@ -155,6 +156,7 @@ class Engine:
         with torch.cuda.device(self.runtime.device):
             batch = build_step_batch(rows, self.cache, self.runtime.device)
             logits = self.model.forward(batch, self.cache)
+        self.h2d_bytes += batch.packed_bytes
         self.cache.commit(slots, lens)
         self.steps_run += 1
         return logits

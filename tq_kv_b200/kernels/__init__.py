@@ -1,9 +1,9 @@
 """Python entry points of the hand-written CUDA kernels (sources in ../csrc)."""
-from ._lib import KernelError
+from ._lib import KernelError, launches
 from .attention import attention, check_head_geometry, plan_splits, split_scratch_floats
 from .elementwise import add_into, embed, qkv_rope_cache, rmsnorm, swiglu
 from .gemm import gemm_tiled, gemv_rows, linear
 from .sampling import sample
 
-__all__ = ["KernelError", "add_into", "attention", "check_head_geometry", "embed", "gemm_tiled", "gemv_rows",
+__all__ = ["KernelError", "add_into", "attention", "check_head_geometry", "embed", "launches", "gemm_tiled", "gemv_rows",
            "linear", "plan_splits", "qkv_rope_cache", "rmsnorm", "sample", "split_scratch_floats", "swiglu"]

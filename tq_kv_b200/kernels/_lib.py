@@ -43,9 +43,14 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def check(status: int, what: str) -> None:
+# How many kernels of this package were launched (a claim the benchmark reports).
+launches = [0]
+
+
+def check(status: int, what: str, n_kernels: int = 1) -> None:
     if status != 0:
         raise KernelError(f"{what}: CUDA error {status}" + (" (invalid argument)" if status == 1 else ""))
+    launches[0] += n_kernels
 
 
 _SIGNATURES = {

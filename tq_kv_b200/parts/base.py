@@ -67,6 +67,7 @@ class StepBatch:
     host_slots: list[int] = field(default_factory=list)
     host_start: list[int] = field(default_factory=list)
     host_lens: list[int] = field(default_factory=list)      # tokens each row brings
+    packed_bytes: int = 0                                    # size of the one host-to-device copy
 
     @property
     def all_from_zero(self) -> bool:
