@@ -115,6 +115,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for profiler captures)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiler captures)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -151,6 +153,7 @@ def main() -> int:
         start_ctx = max(1, args.context - K - W)
 
     engine = tq.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_slots=max_b, max_context=args.context)
+    engine.use_graphs = not args.no_graphs
     gen = torch.Generator().manual_seed(0)
     dev = engine.runtime.device
 
@@ -207,12 +210,14 @@ def main() -> int:
 
     h2d0 = engine.h2d_bytes
     stats: dict = {}
-    engine.generate(prompts, tq.GenerationParams.greedy(e2e_steps + 1, stop_token_ids=()), on_token=on_token,
-                    stats=stats)
-    e2e_value = args.batch * (len(stamps) - 1) / (stamps[-1] - stamps[0])
-    steps_total = len(stamps)
-    h2d = (engine.h2d_bytes - h2d0 + stats.get("h2d_bytes", 0)) / steps_total
-    d2h = stats.get("d2h_bytes", 0) / steps_total
+    e2e_value = h2d = d2h = 0.0
+    if not args.no_e2e:
+        engine.generate(prompts, tq.GenerationParams.greedy(e2e_steps + 1, stop_token_ids=()), on_token=on_token,
+                        stats=stats)
+        e2e_value = args.batch * (len(stamps) - 1) / (stamps[-1] - stamps[0])
+        steps_total = len(stamps)
+        h2d = (engine.h2d_bytes - h2d0 + stats.get("h2d_bytes", 0)) / steps_total
+        d2h = stats.get("d2h_bytes", 0) / steps_total
 
     rec = {
         "metric": "decode tok/s (Qwen2.5-7B shape, bf16 random weights)", "value": round(value, 1),

@@ -27,6 +27,8 @@ def _register():
     from tq_kv_b200.parts import Mixer, WeightSpec, register_part
 
     class RunningMeanMixer(Mixer):
+        graph_capturable = False          # its step reads the batch's layout back to the host
+
         def __init__(self, spec):
             super().__init__(spec)
             self.hidden, self.inner = self.params["hidden_size"], self.params["inner_size"]

@@ -49,7 +49,7 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
                                  const int* __restrict__ tok_seq, const int* __restrict__ cu_seqlens,
                                  const int* __restrict__ start_pos, int window, float scale, TC* __restrict__ out,
                                  float* __restrict__ part_acc, float* __restrict__ part_ml, int nh, int nkv, int hd,
-                                 int n_splits, int split_len) {
+                                 int n_splits) {
     extern __shared__ float q_sh[];   // [n_warps][hd]
     const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -58,9 +58,14 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
     const int b = tok_seq[t];
     const int tok0 = src.k_packed ? cu_seqlens[b] - start_pos[b] : 0;
     const int lo_all = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int lo = lo_all + split * split_len;
-    int hi = pos + 1;                                   // exclusive
-    if (n_splits > 1 && lo + split_len < hi) hi = lo + split_len;
+    int lo = lo_all, hi = pos + 1;                      // [lo, hi): this block's keys
+    if (n_splits > 1) {
+        // every token cuts its own key range into n_splits equal parts (multiples of 32 keys)
+        const int keys = pos + 1 - lo_all;
+        const int split_len = (((keys + n_splits - 1) / n_splits) + 31) & ~31;
+        lo = lo_all + split * split_len;
+        if (lo + split_len < hi) hi = lo + split_len;
+    }
     float* qs = q_sh + warp * hd;
     constexpr int VEC = Vec16<TC>::N;
 
@@ -166,11 +171,10 @@ TQ_API int tq_attention(const void* q, int dtype, const void* k_packed, const vo
                         const void* v_pages, const int* block_table, int table_width, int ring_pages,
                         int page_tokens, const int* tok_pos, const int* tok_seq, const int* cu_seqlens,
                         const int* start_pos, int window, float scale, void* out, float* part_acc, float* part_ml,
-                        int n_tokens, int nh, int nkv, int hd, int n_splits, int split_len, cudaStream_t stream) {
+                        int n_tokens, int nh, int nkv, int hd, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || hd > 64 * ATT_MAX_PAIRS || hd % 16 || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
-    if (n_splits < 1 || (n_splits > 1 && (!part_acc || !part_ml || split_len <= 0 || split_len % 32)))
-        return (int)cudaErrorInvalidValue;
+    if (n_splits < 1 || (n_splits > 1 && (!part_acc || !part_ml))) return (int)cudaErrorInvalidValue;
     if (!k_packed && (!k_pages || !block_table || page_tokens <= 0)) return (int)cudaErrorInvalidValue;
     if (nkv > 65535 || n_splits > 65535) return (int)cudaErrorInvalidValue;
     KVSource src{k_packed, v_packed, k_pages, v_pages, block_table, table_width, ring_pages, page_tokens};
@@ -181,11 +185,11 @@ TQ_API int tq_attention(const void* q, int dtype, const void* k_packed, const vo
     if (dtype == TQ_F32)
         attention_kernel<float><<<grid, n_warps * 32, smem, stream>>>(
             (const float*)q, src, tok_pos, tok_seq, cu_seqlens, start_pos, window, scale, (float*)out, part_acc,
-            part_ml, nh, nkv, hd, n_splits, split_len);
+            part_ml, nh, nkv, hd, n_splits);
     else if (dtype == TQ_BF16)
         attention_kernel<bf16><<<grid, n_warps * 32, smem, stream>>>(
             (const bf16*)q, src, tok_pos, tok_seq, cu_seqlens, start_pos, window, scale, (bf16*)out, part_acc,
-            part_ml, nh, nkv, hd, n_splits, split_len);
+            part_ml, nh, nkv, hd, n_splits);
     else
         return (int)cudaErrorInvalidValue;
     int st = tq_launch_status();
@@ -195,5 +199,20 @@ TQ_API int tq_attention(const void* q, int dtype, const void* k_packed, const vo
         attention_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (float*)out, nh, hd, n_splits);
     else
         attention_merge_kernel<bf16><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (bf16*)out, nh, hd, n_splits);
+    return tq_launch_status();
+}
+
+// The merge step alone, for kernels that write (unnormalised output, max, sum) per split themselves.
+TQ_API int tq_attention_merge(const float* part_acc, const float* part_ml, void* out, int dtype, int n_tokens, int nh,
+                              int hd, int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_splits < 1 || !part_acc || !part_ml) return (int)cudaErrorInvalidValue;
+    const dim3 mgrid(n_tokens, nh);
+    if (dtype == TQ_F32)
+        attention_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (float*)out, nh, hd, n_splits);
+    else if (dtype == TQ_BF16)
+        attention_merge_kernel<bf16><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (bf16*)out, nh, hd, n_splits);
+    else
+        return (int)cudaErrorInvalidValue;
     return tq_launch_status();
 }

@@ -25,7 +25,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 GROUPS: dict[str, list[str]] = {
     # everything a model needs in either precision
-    "core": ["elementwise.cu", "attention.cu", "gemm.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "attention.cu", "flash_decode.cu", "gemm.cu", "skinny_gemm.cu", "sampling.cu"],
 }
 
 NVCC_FLAGS = [
@@ -135,6 +135,12 @@ def build(group: str, verbose_ptxas: bool = False) -> str:
         tmp_so = os.path.join(work, "lib.so")
         _run([nvcc, "-shared", "-o", tmp_so, *objs, "-Xcompiler", "-fPIC", "-lcuda"], f"link {group}")
         os.replace(tmp_so, final)      # atomic: concurrent builders end with the same file
+        for old in os.listdir(out_dir):  # builds of older sources are of no use any more
+            if old.startswith(f"libtqkv_{group}_") and old.endswith(".so") and old != os.path.basename(final):
+                try:
+                    os.remove(os.path.join(out_dir, old))
+                except OSError:
+                    pass
     finally:
         shutil.rmtree(work, ignore_errors=True)
     _say(f"built {os.path.basename(final)} in {time.time() - t0:.0f} s")

@@ -48,14 +48,30 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     __shared__ float red[32];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+    TO* o = out + (size_t)r * H;
     float ss = 0.f;
+    if ((H & 3) == 0) {                       // rows are 16-byte aligned: four values per load
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+        for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+            const float4 v = x4[i];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = block_sum(ss, red);
+        const float rms = sqrtf(ss / (float)H + eps);
+        for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+            const float4 v = x4[i], g = w4[i];
+            store2_f32<TO>(o + 4 * i, (v.x / rms) * g.x, (v.y / rms) * g.y);
+            store2_f32<TO>(o + 4 * i + 2, (v.z / rms) * g.z, (v.w / rms) * g.w);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const float v = xr[i];
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, red);
     const float rms = sqrtf(ss / (float)H + eps);
-    TO* o = out + (size_t)r * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>((xr[i] / rms) * w[i]);
 }
 
@@ -95,83 +111,62 @@ __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* _
                                       int table_width, int ring_pages, int page_tokens, TC* __restrict__ q_out,
                                       TC* __restrict__ k_out, TC* __restrict__ v_out, TC* __restrict__ k_pages,
                                       TC* __restrict__ v_pages, int nh, int nkv, int hd, int rot) {
-    const int t = blockIdx.x;
+    // grid (token, head): heads 0..nh-1 are q, nh..nh+nkv-1 are k, the rest are v
+    const int t = blockIdx.x, head = blockIdx.y;
     const int pos = tok_pos[t];
     const int b = tok_seq[t];
     const int half = rot >> 1;
     const int width = (nh + 2 * nkv) * hd;
-    const TI* x = qkv + (size_t)t * width;
-    const float* cs = cos_tab + (size_t)pos * half;
-    const float* sn = sin_tab + (size_t)pos * half;
+    const TI* x = qkv + (size_t)t * width + (size_t)head * hd;
+    const float* bs = bias ? bias + (size_t)head * hd : nullptr;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    const int g = is_q ? 0 : (is_k ? head - nh : head - nh - nkv);
 
     // where this token's key/value row lives in the cache (or nowhere)
-    size_t cache_row = 0;
-    bool to_cache = k_pages != nullptr;
-    if (to_cache) {
+    TC* cache = nullptr;
+    if (!is_q && k_pages != nullptr) {
         int lp = pos / page_tokens;
+        bool keep = true;
         if (ring_pages > 0) {
-            if (pos < new_lens[b] - ring_pages * page_tokens) to_cache = false;
+            keep = pos >= new_lens[b] - ring_pages * page_tokens;
             lp %= ring_pages;
         }
-        if (to_cache) {
+        if (keep) {
             const int page = block_table[(size_t)b * table_width + lp];
-            cache_row = ((size_t)page * nkv) * page_tokens + (pos % page_tokens);  // + g*page_tokens per head
+            const size_t row = (((size_t)page * nkv + g) * page_tokens + (pos % page_tokens)) * hd;
+            cache = (is_k ? k_pages : v_pages) + row;
         }
     }
-
-    // rotated part of q and k: one thread per (head, j < half)
-    const int n_rot = (nh + nkv) * half;
-    for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
-        const int head = i / half, j = i - head * half;
-        const int c0 = head * hd + j, c1 = c0 + half;
-        float x0 = to_f32<TI>(x[c0]), x1 = to_f32<TI>(x[c1]);
-        if (bias) { x0 += bias[c0]; x1 += bias[c1]; }
-        const float c = cs[j], s = sn[j];
-        const float r0 = x0 * c - x1 * s;
-        const float r1 = x0 * s + x1 * c;
-        if (head < nh) {
-            TC* q = q_out + (size_t)t * nh * hd + head * hd;
-            q[j] = from_f32<TC>(r0);
-            q[j + half] = from_f32<TC>(r1);
-        } else {
-            const int g = head - nh;
-            if (k_out) {
-                TC* k = k_out + ((size_t)t * nkv + g) * hd;
-                k[j] = from_f32<TC>(r0);
-                k[j + half] = from_f32<TC>(r1);
-            }
-            if (to_cache) {
-                TC* k = k_pages + (cache_row + (size_t)g * page_tokens) * hd;
-                k[j] = from_f32<TC>(r0);
-                k[j + half] = from_f32<TC>(r1);
-            }
+    TC* dst = is_q ? q_out + ((size_t)t * nh + head) * hd
+                   : (is_k ? (k_out ? k_out + ((size_t)t * nkv + g) * hd : nullptr)
+                           : (v_out ? v_out + ((size_t)t * nkv + g) * hd : nullptr));
+    if (is_q || is_k) {
+        const float* cs = cos_tab + (size_t)pos * half;
+        const float* sn = sin_tab + (size_t)pos * half;
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            float x0 = to_f32<TI>(x[j]), x1 = to_f32<TI>(x[j + half]);
+            if (bs) { x0 += bs[j]; x1 += bs[j + half]; }
+            const float c = cs[j], s = sn[j];
+            const TC r0 = from_f32<TC>(x0 * c - x1 * s);
+            const TC r1 = from_f32<TC>(x0 * s + x1 * c);
+            if (dst) { dst[j] = r0; dst[j + half] = r1; }
+            if (cache) { cache[j] = r0; cache[j + half] = r1; }
         }
-    }
-    // dims beyond the rotated part of q and k pass through
-    if (rot < hd) {
-        const int rest = hd - rot;
-        for (int i = threadIdx.x; i < (nh + nkv) * rest; i += blockDim.x) {
-            const int head = i / rest, d = rot + (i - head * rest);
-            const int c = head * hd + d;
-            float v = to_f32<TI>(x[c]);
-            if (bias) v += bias[c];
-            if (head < nh) {
-                q_out[(size_t)t * nh * hd + c] = from_f32<TC>(v);
-            } else {
-                const int g = head - nh;
-                if (k_out) k_out[((size_t)t * nkv + g) * hd + d] = from_f32<TC>(v);
-                if (to_cache) k_pages[(cache_row + (size_t)g * page_tokens) * hd + d] = from_f32<TC>(v);
-            }
+        for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) {      // dims beyond the rotated part pass through
+            float v = to_f32<TI>(x[d]);
+            if (bs) v += bs[d];
+            const TC r = from_f32<TC>(v);
+            if (dst) dst[d] = r;
+            if (cache) cache[d] = r;
         }
-    }
-    // values: bias only
-    const int v0 = (nh + nkv) * hd;
-    for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
-        const int g = i / hd, d = i - g * hd;
-        float v = to_f32<TI>(x[v0 + i]);
-        if (bias) v += bias[v0 + i];
-        if (v_out) v_out[(size_t)t * nkv * hd + i] = from_f32<TC>(v);
-        if (to_cache) v_pages[(cache_row + (size_t)g * page_tokens) * hd + d] = from_f32<TC>(v);
+    } else {
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {             // values: bias only
+            float v = to_f32<TI>(x[d]);
+            if (bs) v += bs[d];
+            const TC r = from_f32<TC>(v);
+            if (dst) dst[d] = r;
+            if (cache) cache[d] = r;
+        }
     }
 }
 
@@ -184,9 +179,11 @@ TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, c
     if (rot <= 0 || rot > hd || (rot & 1) || page_tokens <= 0) return (int)cudaErrorInvalidValue;
     if ((k_pages == nullptr) != (v_pages == nullptr)) return (int)cudaErrorInvalidValue;
     if (k_pages && !block_table) return (int)cudaErrorInvalidValue;
-    const int threads = 128;
+    if (nh + 2 * nkv > 65535) return (int)cudaErrorInvalidValue;
+    const int threads = hd >= 128 ? 64 : 32;
+    const dim3 grid(n_tokens, nh + 2 * nkv);
 #define TQ_LAUNCH(TI, TC)                                                                                       \
-    qkv_rope_cache_kernel<TI, TC><<<n_tokens, threads, 0, stream>>>(                                           \
+    qkv_rope_cache_kernel<TI, TC><<<grid, threads, 0, stream>>>(                                           \
         (const TI*)qkv, bias, cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width,          \
         ring_pages, page_tokens, (TC*)q_out, (TC*)k_out, (TC*)v_out, (TC*)k_pages, (TC*)v_pages, nh, nkv, hd, rot)
     if (in_dtype == TQ_F32 && cache_dtype == TQ_F32) TQ_LAUNCH(float, float);

@@ -1,0 +1,222 @@
+// Weight-streaming matrix product for decoding: Y[M,N] = X[M,K] · W[N,K]^T
+// with M <= 64 rows of activations, bfloat16 operands, float32 accumulation
+// on the tensor cores (mma.sync m16n8k16: W rows are the "M" side of the
+// instruction, the batch is its "N" side).  The kernel is bound by reading W
+// once from HBM; everything is arranged so that each lane loads 16 contiguous
+// bytes of a W row and many such loads are in flight.
+//
+// Work split: a block owns 16 (or 32) output columns, its 8 warps split K and
+// add their partial sums through shared memory in warp order.  Where that
+// gives too few blocks to fill the GPU (few columns, long K), a thread-block
+// cluster of 2, 4 or 8 blocks splits K once more and the cluster's first
+// block adds the others' sums, read from their shared memory in rank order.
+// So the result never depends on scheduling.  Epilogues: bias, SwiGLU gating (W holds the
+// gate rows, then the up rows: src/models/turbo_generic.rs:105-110), adding
+// into the float32 residual stream (:1969, :1980), float32 or bfloat16 output.
+//
+// The k index inside a 32-wide block is permuted the same way for both
+// operands (lane tid4 owns k = 8*tid4 .. 8*tid4+7 and feeds elements 0..3 to
+// one mma and 4..7 to the next), which leaves every dot product unchanged.
+#include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
+#define SK_WARPS 8
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// NT: tiles of 8 batch rows (M <= 8*NT).  TW: W row tiles of 16 per warp (1 or 2).
+// SWIGLU: TW must be 2; tile 0 = gate rows n, tile 1 = up rows n + N.
+template <int NT, int TW, bool SWIGLU, typename TO>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+skinny_gemm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias,
+                   TO* __restrict__ Y, int M, int N, int K, int ldx, int ldw, int ldy, int accumulate) {
+    constexpr int COLS = SWIGLU ? 16 : 16 * TW;          // output columns of this block
+    extern __shared__ float red_raw[];
+    float (*red)[TW][16][8 * NT + 1] = reinterpret_cast<float (*)[TW][16][8 * NT + 1]>(red_raw);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gid = lane >> 2, tid4 = lane & 3;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int n_ranks = (int)cluster.num_blocks();       // blocks that share these columns and split K
+    const int rank = (int)cluster.block_rank();
+    const int col0 = (blockIdx.x / n_ranks) * COLS;
+
+    // rows of W this lane reads (clamped; masked at the store)
+    const bf16* wp[TW][2];
+#pragma unroll
+    for (int t = 0; t < TW; ++t) {
+        const int base = SWIGLU ? (col0 + t * N) : (col0 + 16 * t);
+        const int limit = SWIGLU ? (t + 1) * N : N;
+        int r0 = base + gid, r1 = base + gid + 8;
+        r0 = r0 < limit ? r0 : limit - 1;
+        r1 = r1 < limit ? r1 : limit - 1;
+        wp[t][0] = W + (size_t)r0 * ldw + tid4 * 8;
+        wp[t][1] = W + (size_t)r1 * ldw + tid4 * 8;
+    }
+    const bf16* xp[NT];
+    bool xv[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        const int m = n * 8 + gid;
+        xv[n] = m < M;
+        xp[n] = X + (size_t)(xv[n] ? m : 0) * ldx + tid4 * 8;
+    }
+    float acc[TW][NT][4];
+#pragma unroll
+    for (int t = 0; t < TW; ++t)
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[t][n][i] = 0.f;
+
+    const int kblocks = K >> 5;
+    const int parts = SK_WARPS * n_ranks;
+    const int per = (kblocks + parts - 1) / parts;
+    const int kb0 = min(kblocks, (rank * SK_WARPS + warp) * per);
+    const int kb1 = min(kblocks, kb0 + per);
+#pragma unroll 4
+    for (int kb = kb0; kb < kb1; ++kb) {
+        const int k = kb << 5;
+        uint4 a[TW][2];
+#pragma unroll
+        for (int t = 0; t < TW; ++t) {
+            a[t][0] = ld_stream16(wp[t][0] + k);
+            a[t][1] = ld_stream16(wp[t][1] + k);
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (xv[n]) b = *reinterpret_cast<const uint4*>(xp[n] + k);
+#pragma unroll
+            for (int t = 0; t < TW; ++t) {
+                mma_bf16_16816(acc[t][n], a[t][0].x, a[t][1].x, a[t][0].y, a[t][1].y, b.x, b.y);
+                mma_bf16_16816(acc[t][n], a[t][0].z, a[t][1].z, a[t][0].w, a[t][1].w, b.z, b.w);
+            }
+        }
+    }
+    // partial sums of this warp: c0,c1 -> (row gid, batch 2*tid4, +1); c2,c3 -> (row gid+8, same)
+#pragma unroll
+    for (int t = 0; t < TW; ++t)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            red[warp][t][gid][n * 8 + 2 * tid4] = acc[t][n][0];
+            red[warp][t][gid][n * 8 + 2 * tid4 + 1] = acc[t][n][1];
+            red[warp][t][gid + 8][n * 8 + 2 * tid4] = acc[t][n][2];
+            red[warp][t][gid + 8][n * 8 + 2 * tid4 + 1] = acc[t][n][3];
+        }
+    __syncthreads();
+    // block sums: warps added in order into red[0]
+    constexpr int PER_WARP = TW * 16 * (8 * NT + 1);
+    for (int e = threadIdx.x; e < PER_WARP; e += blockDim.x) {
+        float v = red_raw[e];
+#pragma unroll
+        for (int w = 1; w < SK_WARPS; ++w) v += red_raw[w * PER_WARP + e];
+        red_raw[e] = v;
+    }
+    if (n_ranks > 1) cluster.sync(); else __syncthreads();
+    if (rank == 0) {
+        // one thread per (column, batch row): the cluster's blocks added in rank order, then the epilogue
+        for (int e = threadIdx.x; e < COLS * 8 * NT; e += blockDim.x) {
+            const int m = e / COLS, c = e - m * COLS;      // consecutive threads -> consecutive columns
+            if (m >= M) continue;
+            const int col = col0 + c;
+            if (col >= N) continue;
+            const int t = SWIGLU ? 0 : (c >> 4), r = SWIGLU ? c : (c & 15);
+            float v = red[0][t][r][m], u = SWIGLU ? red[0][TW - 1][r][m] : 0.f;
+            for (int p = 1; p < n_ranks; ++p) {
+                const float* peer = cluster.map_shared_rank(red_raw, p);
+                v += peer[(t * 16 + r) * (8 * NT + 1) + m];
+                if (SWIGLU) u += peer[((TW - 1) * 16 + r) * (8 * NT + 1) + m];
+            }
+            if (bias) { v += bias[col]; if (SWIGLU) u += bias[col + N]; }
+            if (SWIGLU) v = (v / (1.f + expf(-v))) * u;
+            TO* y = Y + (size_t)m * ldy + col;
+            if (accumulate) v += to_f32<TO>(*y);
+            *y = from_f32<TO>(v);
+        }
+    }
+    if (n_ranks > 1) cluster.sync();                       // peers keep their shared memory until it was read
+}
+
+template <int NT, int TW, bool SWIGLU, typename TO>
+static int launch_skinny(const bf16* X, const bf16* W, const float* bias, void* Y, int M, int N, int K, int ldx,
+                         int ldw, int ldy, int accumulate, cudaStream_t stream) {
+    constexpr int COLS = SWIGLU ? 16 : 16 * TW;
+    const int tiles = (N + COLS - 1) / COLS;
+    // split K over a cluster while the grid is small and every warp keeps a few k-blocks
+    int ranks = 1;
+    while (ranks < 8 && tiles * ranks < 4 * 148 && (K >> 5) / (SK_WARPS * ranks * 2) >= 4) ranks *= 2;
+    constexpr size_t smem = sizeof(float) * SK_WARPS * TW * 16 * (8 * NT + 1);
+    static bool configured = false;          // per template instance
+    if (smem > 48 * 1024 && !configured) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, TW, SWIGLU, TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * ranks, 1, 1);
+    cfg.blockDim = dim3(SK_WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TW, SWIGLU, TO>, X, W, bias, (TO*)Y, M, N, K, ldx,
+                                       ldw, ldy, accumulate);
+    if (e != cudaSuccess) return (int)e;
+    return tq_launch_status();
+}
+
+template <bool SWIGLU, typename TO>
+static int dispatch_skinny(const bf16* X, const bf16* W, const float* bias, void* Y, int M, int N, int K, int ldx,
+                           int ldw, int ldy, int accumulate, cudaStream_t s) {
+    if (SWIGLU) {
+        if (M <= 8) return launch_skinny<1, 2, true, TO>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, s);
+        if (M <= 16) return launch_skinny<2, 2, true, TO>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, s);
+        if (M <= 32) return launch_skinny<4, 2, true, TO>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, s);
+        return launch_skinny<8, 2, true, TO>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, s);
+    }
+    if (M <= 8) return launch_skinny<1, 1, false, TO>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, s);
+    if (M <= 16) return launch_skinny<2, 1, false, TO>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, s);
+    if (M <= 32) return launch_skinny<4, 2, false, TO>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, s);
+    return launch_skinny<8, 2, false, TO>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, s);
+}
+
+// X [M, K] bf16, W [N, K] (or [2N, K] with swiglu) bf16, Y [M, N] float32 or
+// bfloat16.  Needs M <= 64, K a multiple of 32, 16-byte aligned rows.
+TQ_API int tq_skinny_gemm(const void* X, const void* W, const float* bias, void* Y, int y_dtype, int M, int N, int K,
+                          int ldx, int ldw, int ldy, int accumulate, int swiglu, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K <= 0 || (K & 31) || (ldx & 7) || (ldw & 7)) return (int)cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+        return (int)cudaErrorInvalidValue;
+    if (accumulate && y_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    const bf16* x = (const bf16*)X;
+    const bf16* w = (const bf16*)W;
+    if (swiglu) {
+        if (y_dtype == TQ_F32) return dispatch_skinny<true, float>(x, w, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
+        if (y_dtype == TQ_BF16) return dispatch_skinny<true, bf16>(x, w, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
+    } else {
+        if (y_dtype == TQ_F32) return dispatch_skinny<false, float>(x, w, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
+        if (y_dtype == TQ_BF16) return dispatch_skinny<false, bf16>(x, w, bias, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
+    }
+    return (int)cudaErrorInvalidValue;
+}

@@ -1,0 +1,113 @@
+"""Decode steps as replayed CUDA graphs.
+
+A decode step of B sequences launches a few hundred small kernels; launching
+them from Python costs more than running them.  For each batch size the step
+is therefore captured once into a CUDA graph over static buffers (the packed
+step metadata with block tables of full width, the logits) and replayed:
+per step, the host fills one pinned staging buffer, copies it to the device
+and replays.  Staging buffers form a small ring, each guarded by an event, so
+that the host may run a few steps ahead of the device.
+
+The captured step is the same `DecoderModel.forward` that an uncaptured step
+runs; only planning inputs are frozen: attention plans its splits for the
+context limit (each token still cuts its own key range evenly).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache import SequenceCache
+from ..parts import StepBatch
+from .batch import _pad4
+
+
+class DecodeGraph:
+    RING = 4
+
+    def __init__(self, model, cache: SequenceCache, runtime, B: int):
+        self.model, self.cache, self.B = model, cache, B
+        dev = runtime.device
+        self.widths = []
+        for g in cache.groups:
+            full = -(-runtime.max_context // g.book.page_tokens)
+            self.widths.append(min(full, g.book.ring_pages) if g.book.ring_pages else full)
+        seg = [B, B, B, B + 1, B, B, B, B] + [B * w for w in self.widths]
+        self.offs, total = [], 0
+        for s in seg:
+            self.offs.append(total)
+            total += _pad4(s)
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        self.host = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.events = [None] * self.RING
+        self.turn = 0
+        o = self.offs
+        arange = np.arange(B + 1, dtype=np.int32)
+        for h in self.host:                                   # the parts of the layout that never change
+            a = h.numpy()
+            a[o[1]:o[1] + B] = arange[:B]                     # tok_seq
+            a[o[3]:o[3] + B + 1] = arange                     # cu_seqlens
+            a[o[7]:o[7] + B] = arange[:B]                     # logit_rows: every row
+        d = self.dev
+
+        def seg_view(i, n):
+            return d[o[i]:o[i] + n]
+
+        self.batch = StepBatch(
+            n_tokens=B, n_seqs=B, tokens=seg_view(0, B), tok_seq=seg_view(1, B), tok_pos=seg_view(2, B),
+            cu_seqlens=seg_view(3, B + 1), slots=seg_view(4, B), start_pos=seg_view(5, B), new_lens=seg_view(6, B),
+            logit_rows=seg_view(7, B), n_logit_rows=B,
+            block_tables=[(seg_view(8 + gi, B * w), w) for gi, w in enumerate(self.widths)],
+            host_slots=[0] * B, host_start=[1] * B, host_lens=[1] * B, packed_bytes=total * 4,
+            plan_max_len=runtime.max_context)
+        self.graph = None
+        self.logits = None
+        self.kernels_per_replay = 0
+
+    def _fill(self, rows) -> torch.Tensor:
+        i = self.turn % self.RING
+        self.turn += 1
+        if self.events[i] is not None:
+            self.events[i].synchronize()                      # the copy that last used this buffer is done
+        h = self.host[i]
+        a = h.numpy()
+        o, B, cache = self.offs, self.B, self.cache
+        slots = [r.slot for r in rows]
+        starts = [cache.length(s) for s in slots]
+        a[o[0]:o[0] + B] = [r.tokens[0] for r in rows]
+        a[o[2]:o[2] + B] = starts
+        a[o[4]:o[4] + B] = slots
+        a[o[5]:o[5] + B] = starts
+        a[o[6]:o[6] + B] = [s + 1 for s in starts]
+        for gi, w in enumerate(self.widths):
+            trows, _ = cache.block_table_rows(gi, slots)
+            base = o[8 + gi]
+            for b, pages in enumerate(trows):
+                a[base + b * w: base + b * w + len(pages)] = pages
+        self.batch.host_slots = slots
+        self.dev.copy_(h, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return h
+
+    def run(self, rows) -> torch.Tensor:
+        """Runs one decode step for `rows` (already reserved in the cache);
+        returns float32 logits [B, vocab] (a copy of the graph's static output)."""
+        from .. import kernels
+        self._fill(rows)
+        if self.graph is None:
+            # first use: one plain run to warm allocators and libraries, then the capture of a second run
+            # (both write the same cache rows with the same values)
+            n0 = kernels.launches[0]
+            self.model.forward(self.batch, self.cache)
+            self.kernels_per_replay = kernels.launches[0] - n0
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.logits = self.model.forward(self.batch, self.cache)
+            kernels.launches[0] -= self.kernels_per_replay     # capturing launched nothing
+            self.graph = g
+        self.graph.replay()
+        kernels.launches[0] += self.kernels_per_replay
+        return self.logits.clone()

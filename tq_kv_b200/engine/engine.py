@@ -22,6 +22,7 @@ from ..parts import Runtime
 from ..weights import load_tensors, random_tensors
 from ..weights.random_init import storage_dtype
 from .batch import StepRow, build_step_batch
+from .decode_graph import DecodeGraph
 from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -46,6 +47,8 @@ class Engine:
         self.spec = model.spec
         self.vocab_size = model.spec.vocab_size
         self.steps_run = 0
+        self.use_graphs = model.graph_capturable      # replay captured CUDA graphs for decode steps
+        self._decode_graphs: dict[int, "DecodeGraph"] = {}
         self.h2d_bytes = 0            # bytes of step inputs copied to the device so far
 
     # ---- construction -------------------------------------------------------
@@ -154,9 +157,17 @@ class Engine:
         except CacheError as e:
             raise StepError(str(e)) from e
         with torch.cuda.device(self.runtime.device):
-            batch = build_step_batch(rows, self.cache, self.runtime.device)
-            logits = self.model.forward(batch, self.cache)
-        self.h2d_bytes += batch.packed_bytes
+            if self.use_graphs and all(n == 1 for n in lens) and all(r.want == [0] for r in rows):
+                graph = self._decode_graphs.get(len(rows))
+                if graph is None:
+                    graph = self._decode_graphs[len(rows)] = DecodeGraph(self.model, self.cache, self.runtime,
+                                                                         len(rows))
+                logits = graph.run(rows)
+                self.h2d_bytes += graph.batch.packed_bytes
+            else:
+                batch = build_step_batch(rows, self.cache, self.runtime.device)
+                logits = self.model.forward(batch, self.cache)
+                self.h2d_bytes += batch.packed_bytes
         self.cache.commit(slots, lens)
         self.steps_run += 1
         return logits

@@ -39,6 +39,10 @@ class DecoderModel:
         yield self.final_norm
         yield self.head
 
+    @property
+    def graph_capturable(self) -> bool:
+        return all(getattr(p, "graph_capturable", True) for p in self._all_parts())
+
     def weight_specs(self) -> dict[str, WeightSpec]:
         """Every tensor the model expects, by name.  Two parts may name the
         same tensor (a tied head) if they agree on its shape."""

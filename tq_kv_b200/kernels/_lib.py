@@ -63,11 +63,16 @@ _SIGNATURES = {
     "tq_add_into": [c_void_p, c_void_p, c_int, c_size_t, c_void_p],
     "tq_attention": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
-                     c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                     c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_gemm_tiled": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                       c_int, c_int, c_int, c_void_p],
     "tq_gemv_rows": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                      c_int, c_int, c_int, c_int, c_void_p],
+    "tq_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                       c_int, c_int, c_void_p],
+    "tq_flash_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                        c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_attention_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p,
                   c_void_p],
 }

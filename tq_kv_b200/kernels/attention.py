@@ -9,6 +9,7 @@ import torch
 from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream
 
 MAX_HEAD_DIM = 256
+NOT_SUPPORTED = 801     # cudaErrorNotSupported: a specialised kernel declines the shape
 
 
 def check_head_geometry(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
@@ -21,20 +22,17 @@ def check_head_geometry(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
         raise KernelError(f"attention: more than 65535 key/value heads ({n_kv_heads})")
 
 
-def plan_splits(n_tokens: int, n_kv_heads: int, max_keys: int, sm_count: int = 148) -> tuple[int, int]:
-    """(n_splits, split_len) for a step: one split while the grid fills the
-    GPU or the key ranges are short, else enough splits of a multiple of 32
-    keys to give every SM a few blocks."""
+def plan_splits(n_tokens: int, n_kv_heads: int, max_keys: int, sm_count: int = 148) -> int:
+    """Number of splits of the key range for a step: one while the grid fills
+    the GPU or the key ranges are short, else as many as fill the GPU in one
+    wave, with at least 128 keys per split of the longest range.  (Each
+    token cuts its own range into that many equal parts.)"""
     blocks = n_tokens * n_kv_heads
-    if blocks >= 2 * sm_count or max_keys <= 512:
-        return 1, 0
-    want = min(-(-4 * sm_count // blocks), -(-max_keys // 256), 64)
-    if want <= 1:
-        return 1, 0
-    split_len = -(-max_keys // want)
-    split_len = -(-split_len // 32) * 32
-    n_splits = -(-max_keys // split_len)
-    return (n_splits, split_len) if n_splits > 1 else (1, 0)
+    resident = 2 * sm_count                    # blocks of the decode kernel that run at once
+    if blocks >= resident or max_keys <= 256:
+        return 1
+    # fill the GPU once: a grid a little over a whole number of waves wastes most of its last wave
+    return max(1, min(resident // blocks, -(-max_keys // 128), 64))
 
 
 def split_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
@@ -47,8 +45,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: i
               k_packed: Optional[torch.Tensor] = None, v_packed: Optional[torch.Tensor] = None,
               k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
               block_table: Optional[torch.Tensor] = None, table_width: int = 0, ring_pages: int = 0,
-              page_tokens: int = 64, n_splits: int = 1, split_len: int = 0,
-              scratch: Optional[torch.Tensor] = None):
+              page_tokens: int = 64, n_splits: int = 1,
+              scratch: Optional[torch.Tensor] = None, use_flash_decode: bool = True):
     """out[t, h] = softmax(q[t, h] · K / sqrt(head_dim)) · V over the keys
     max(0, pos-window+1) .. pos of the token's sequence.  q/out [T, nh*hd].
     Keys and values come from the step's packed rows (k_packed/v_packed
@@ -78,9 +76,21 @@ def attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: i
                     block_table=block_table)
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
+    if not packed and q.dtype == torch.bfloat16 and use_flash_decode:
+        # the bandwidth-built kernel for the cache; it declines shapes outside its reach
+        st = core().tq_flash_decode(
+            ptr(q), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width, ring_pages, page_tokens,
+            ptr(tok_pos), ptr(tok_seq), int(window or 0), float(scale), ptr(out), ptr(part_acc), ptr(part_ml), T,
+            n_heads, n_kv_heads, head_dim, n_splits, stream())
+        if st != NOT_SUPPORTED:
+            check(st, "flash_decode")
+            if n_splits > 1:
+                check(core().tq_attention_merge(ptr(part_acc), ptr(part_ml), ptr(out), dtype_code(out), T, n_heads,
+                                                head_dim, n_splits, stream()), "attention_merge")
+            return out
     check(core().tq_attention(
         ptr(q), dtype_code(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table),
         table_width, ring_pages, page_tokens, ptr(tok_pos), ptr(tok_seq), ptr(cu_seqlens), ptr(start_pos),
         int(window or 0), float(scale), ptr(out), ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, head_dim,
-        n_splits, split_len, stream()), "attention", 2 if n_splits > 1 else 1)
+        n_splits, stream()), "attention", 2 if n_splits > 1 else 1)
     return out

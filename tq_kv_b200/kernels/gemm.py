@@ -1,9 +1,11 @@
 """Matrix products: y = x · W^T with W stored [out, in].
 
 `linear()` picks the kernel from the operands:
-  * few rows (decoding): the hand-written row kernel of csrc/gemm.cu, which
-    streams the weight once per 8 rows and fuses bias, SwiGLU gating and the
-    float32 accumulation into the residual stream;
+  * up to 64 rows of bfloat16 (decoding): the weight-streaming tensor-core
+    kernel of csrc/skinny_gemm.cu, which reads the weight once and fuses bias,
+    SwiGLU gating and the float32 accumulation into the residual stream;
+  * up to 16 rows of anything else: the float32 row kernel of csrc/gemm.cu
+    with the same epilogues;
   * many rows, bfloat16 × bfloat16: the library matrix product (cuBLAS through
     torch.mm with float32 output), as the reference engine does for all its
     products (src/models/turbo_generic.rs:68-91 -> candle -> cuBLAS);
@@ -20,6 +22,24 @@ from . import elementwise
 from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream
 
 ROW_KERNEL_MAX_ROWS = 16
+SKINNY_MAX_ROWS = 64
+
+
+def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
+    """bfloat16 x [M <= 64, K] times bfloat16 w [N, K]^T on the tensor cores,
+    streaming w once (csrc/skinny_gemm.cu).  K must be a multiple of 32."""
+    M, K = x.shape
+    N = out.shape[1]
+    check(core().tq_skinny_gemm(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0),
+                                w.stride(0), out.stride(0), int(accumulate), int(swiglu), stream()), "skinny_gemm")
+    return out
+
+
+def _skinny_ok(x, w) -> bool:
+    K = x.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS
+            and K % 32 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def gemm_tiled(x, w, out, bias=None, accumulate=False):
@@ -68,6 +88,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
     if M == 0:
         return out
 
+    if _skinny_ok(x, w):
+        return skinny_gemm(x, w, out, bias, accumulate, swiglu)
     if M <= ROW_KERNEL_MAX_ROWS:
         return gemv_rows(x, w, out, bias, accumulate, swiglu)
 

@@ -110,12 +110,12 @@ class GQAttention(Mixer):
             kernels.attention(q, out, k_packed=k, v_packed=v, **common)
         else:
             max_keys = b.max_new_len if self.window is None else min(b.max_new_len, self.window)
-            n_splits, split_len = kernels.plan_splits(T, self.n_kv_heads, max_keys, ctx.runtime.sm_count)
+            n_splits = kernels.plan_splits(T, self.n_kv_heads, max_keys, ctx.runtime.sm_count)
             scratch = None
             if n_splits > 1:
                 scratch = torch.empty(kernels.split_scratch_floats(T, self.n_heads, self.head_dim, n_splits),
                                       dtype=torch.float32, device=dev)
             kernels.attention(q, out, k_pages=kv.k_pages, v_pages=kv.v_pages, block_table=kv.block_table,
                               table_width=kv.table_width, ring_pages=kv.ring_pages, page_tokens=kv.page_tokens,
-                              n_splits=n_splits, split_len=split_len, scratch=scratch, **common)
+                              n_splits=n_splits, scratch=scratch, **common)
         kernels.linear(out, self.w_o, bias=self.b_o, out=residual, accumulate=True)

@@ -68,6 +68,7 @@ class StepBatch:
     host_start: list[int] = field(default_factory=list)
     host_lens: list[int] = field(default_factory=list)      # tokens each row brings
     packed_bytes: int = 0                                    # size of the one host-to-device copy
+    plan_max_len: int = 0      # if > 0: the length to plan for instead of this step's own (replayed graphs)
 
     @property
     def all_from_zero(self) -> bool:
@@ -79,6 +80,9 @@ class StepBatch:
 
     @property
     def max_new_len(self) -> int:
+        """Longest sequence after this step, for planning (grids, splits)."""
+        if self.plan_max_len > 0:
+            return self.plan_max_len
         return max(s + n for s, n in zip(self.host_start, self.host_lens))
 
 
@@ -93,6 +97,11 @@ class StepContext:
 
 class Part:
     """Base of all parts."""
+
+    # A part whose step needs the host (reads device data back, branches on
+    # it) sets this to False; the engine then launches that model's decode
+    # steps kernel by kernel instead of replaying a captured CUDA graph.
+    graph_capturable = True
 
     def __init__(self, spec: PartSpec):
         self.spec = spec
