@@ -237,19 +237,24 @@ def plain_attention(q, k, v, nh, nkv, hd, window, q_pos):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(7, 1, 128, None), (6, 3, 48, 20), (5, 5, 16, None), (16, 2, 256, 33),
-                                              (24, 2, 80, None)])
-def test_attention_over_packed_prompts(dtype, nh, nkv, hd, window):
+                                              (24, 2, 80, None), (4, 2, 64, 70), (3, 3, 96, None), (2, 1, 32, 5),
+                                              (14, 2, 128, 129)])
+@pytest.mark.parametrize("lens", [[1, 37, 90], [200, 64, 3, 129]])
+@pytest.mark.parametrize("flash", [True, False])
+def test_attention_over_packed_prompts(dtype, nh, nkv, hd, window, lens, flash):
     from tq_kv_b200 import kernels
-    lens = [1, 37, 90]
     T = sum(lens)
     q, k, v = rnd(T, nh * hd, dtype=dtype), rnd(T, nkv * hd, dtype=dtype, seed=1), rnd(T, nkv * hd, dtype=dtype, seed=2)
-    cu = [0, 1, 38, 128]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
     tok_seq = torch.tensor(sum(([b] * n for b, n in enumerate(lens)), []), dtype=torch.int32, device=DEV)
     tok_pos = torch.tensor(sum((list(range(n)) for n in lens), []), dtype=torch.int32, device=DEV)
     out = torch.empty_like(q)
     kernels.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd, tok_pos=tok_pos, tok_seq=tok_seq,
                       cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV),
-                      start_pos=torch.zeros(3, dtype=torch.int32, device=DEV), window=window, k_packed=k, v_packed=v)
+                      start_pos=torch.zeros(len(lens), dtype=torch.int32, device=DEV), window=window, k_packed=k,
+                      v_packed=v, use_flash=flash)
     for b, n in enumerate(lens):
         a, e = cu[b], cu[b + 1]
         want = plain_attention(q[a:e].cpu(), k[a:e].cpu(), v[a:e].cpu(), nh, nkv, hd, window, list(range(n)))
@@ -290,7 +295,7 @@ def test_attention_over_the_paged_cache_with_splits(dtype, nh, nkv, hd, window, 
                       cu_seqlens=torch.arange(B + 1, dtype=torch.int32, device=DEV),
                       start_pos=torch.tensor(q_pos, dtype=torch.int32, device=DEV), window=window,
                       k_pages=kp, v_pages=vp, block_table=table, table_width=len(table_row),
-                      n_splits=n_splits, scratch=scratch, use_flash_decode=flash)
+                      n_splits=n_splits, scratch=scratch, use_flash=flash)
     want = torch.cat([plain_attention(q[b:b + 1].cpu(), k[:p + 1].cpu(), v[:p + 1].cpu(), nh, nkv, hd, window, [p])
                       for b, p in enumerate(q_pos)])
     close(out, want, 2e-6 if dtype == torch.float32 else 8e-3, "paged")
@@ -328,6 +333,43 @@ def test_a_far_key_among_hundreds_is_found(n_splits, dtype):
     assert float((out.float() - 5.0).abs().max()) < 1e-3
     kernels.attention(q, out, window=696, **args)
     assert float(out.float().abs().max()) < 1.0
+
+
+def test_prompt_chunks_attend_over_the_paged_cache():
+    dtype = torch.bfloat16
+    # Two sequences continued by 70 and 9 tokens at positions 130 and 64: the
+    # 64-query kernel reads earlier keys (and the chunk's own) from the pages.
+    from tq_kv_b200 import kernels
+    nh, nkv, hd, P = 6, 2, 64, 64
+    starts, lens = [130, 64], [70, 9]
+    ks = [rnd(s + n, nkv * hd, dtype=dtype, seed=10 + i) for i, (s, n) in enumerate(zip(starts, lens))]
+    vs = [rnd(s + n, nkv * hd, dtype=dtype, seed=20 + i) for i, (s, n) in enumerate(zip(starts, lens))]
+    tables = [[5, 2, 7, 0], [1, 6, 3, 4]]
+    kp = torch.full((8, nkv, P, hd), 1e4, dtype=dtype, device=DEV)
+    vp = torch.full_like(kp, 1e4)
+    for b in range(2):
+        for j in range(ks[b].shape[0]):
+            kp[tables[b][j // P], :, j % P] = ks[b][j].reshape(nkv, hd)
+            vp[tables[b][j // P], :, j % P] = vs[b][j].reshape(nkv, hd)
+    T = sum(lens)
+    q = rnd(T, nh * hd, dtype=dtype)
+    pos = sum((list(range(s, s + n)) for s, n in zip(starts, lens)), [])
+    for window in (None, 100):
+        for flash in (True, False):
+            out = torch.empty_like(q)
+            kernels.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                              tok_pos=torch.tensor(pos, dtype=torch.int32, device=DEV),
+                              tok_seq=torch.tensor([0] * 70 + [1] * 9, dtype=torch.int32, device=DEV),
+                              cu_seqlens=torch.tensor([0, 70, 79], dtype=torch.int32, device=DEV),
+                              start_pos=torch.tensor(starts, dtype=torch.int32, device=DEV), window=window,
+                              k_pages=kp, v_pages=vp, block_table=torch.tensor(tables, dtype=torch.int32, device=DEV),
+                              table_width=4, use_flash=flash)
+            a = 0
+            for b in range(2):
+                want = plain_attention(q[a:a + lens[b]].cpu(), ks[b].cpu(), vs[b].cpu(), nh, nkv, hd, window,
+                                       list(range(starts[b], starts[b] + lens[b])))
+                close(out[a:a + lens[b]], want, 8e-3, f"row {b}, window {window}, flash {flash}")
+                a += lens[b]
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 8e-3)])

@@ -25,7 +25,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 GROUPS: dict[str, list[str]] = {
     # everything a model needs in either precision
-    "core": ["elementwise.cu", "attention.cu", "flash_decode.cu", "gemm.cu", "skinny_gemm.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "attention.cu", "flash_decode.cu", "flash_prefill.cu", "gemm.cu", "skinny_gemm.cu", "sampling.cu"],
 }
 
 NVCC_FLAGS = [

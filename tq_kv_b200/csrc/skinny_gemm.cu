@@ -25,7 +25,7 @@ namespace cg = cooperative_groups;
 
 __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -33,7 +33,8 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+    // not volatile: the weights are read-only, so the compiler may hoist these loads ahead of the math
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
@@ -87,23 +88,40 @@ skinny_gemm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
     const int per = (kblocks + parts - 1) / parts;
     const int kb0 = min(kblocks, (rank * SK_WARPS + warp) * per);
     const int kb1 = min(kblocks, kb0 + per);
-#pragma unroll 4
-    for (int kb = kb0; kb < kb1; ++kb) {
-        const int k = kb << 5;
-        uint4 a[TW][2];
+    // U k-blocks per turn: all their weight loads are issued before the first mma needs one
+    constexpr int U = (NT <= 2) ? 4 : 2;
+    for (int kb = kb0; kb < kb1; kb += U) {
+        uint4 a[U][TW][2];
+        uint4 bx[U][NT <= 2 ? NT : 1];
 #pragma unroll
-        for (int t = 0; t < TW; ++t) {
-            a[t][0] = ld_stream16(wp[t][0] + k);
-            a[t][1] = ld_stream16(wp[t][1] + k);
-        }
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            uint4 b = make_uint4(0, 0, 0, 0);
-            if (xv[n]) b = *reinterpret_cast<const uint4*>(xp[n] + k);
+        for (int u = 0; u < U; ++u) {
+            const bool on = kb + u < kb1;
+            const int k = (on ? kb + u : kb) << 5;
 #pragma unroll
             for (int t = 0; t < TW; ++t) {
-                mma_bf16_16816(acc[t][n], a[t][0].x, a[t][1].x, a[t][0].y, a[t][1].y, b.x, b.y);
-                mma_bf16_16816(acc[t][n], a[t][0].z, a[t][1].z, a[t][0].w, a[t][1].w, b.z, b.w);
+                a[u][t][0] = ld_stream16(wp[t][0] + k);
+                a[u][t][1] = ld_stream16(wp[t][1] + k);
+                if (!on) a[u][t][0] = a[u][t][1] = make_uint4(0, 0, 0, 0);
+            }
+            if (NT <= 2) {
+#pragma unroll
+                for (int n = 0; n < (NT <= 2 ? NT : 1); ++n)
+                    bx[u][n] = xv[n] ? *reinterpret_cast<const uint4*>(xp[n] + k) : make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (kb + u < kb1 ? kb + u : kb) << 5;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                uint4 b;
+                if (NT <= 2) b = bx[u][n < 2 ? n : 0];
+                else b = xv[n] ? *reinterpret_cast<const uint4*>(xp[n] + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int t = 0; t < TW; ++t) {
+                    mma_bf16_16816(acc[t][n], a[u][t][0].x, a[u][t][1].x, a[u][t][0].y, a[u][t][1].y, b.x, b.y);
+                    mma_bf16_16816(acc[t][n], a[u][t][0].z, a[u][t][1].z, a[u][t][0].w, a[u][t][1].w, b.z, b.w);
+                }
             }
         }
     }

@@ -46,7 +46,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: i
               k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
               block_table: Optional[torch.Tensor] = None, table_width: int = 0, ring_pages: int = 0,
               page_tokens: int = 64, n_splits: int = 1,
-              scratch: Optional[torch.Tensor] = None, use_flash_decode: bool = True):
+              scratch: Optional[torch.Tensor] = None, use_flash: bool = True):
     """out[t, h] = softmax(q[t, h] · K / sqrt(head_dim)) · V over the keys
     max(0, pos-window+1) .. pos of the token's sequence.  q/out [T, nh*hd].
     Keys and values come from the step's packed rows (k_packed/v_packed
@@ -76,7 +76,17 @@ def attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: i
                     block_table=block_table)
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
-    if not packed and q.dtype == torch.bfloat16 and use_flash_decode:
+    n_seqs = cu_seqlens.shape[0] - 1
+    if q.dtype == torch.bfloat16 and use_flash and T > n_seqs:
+        # prompts (some sequence brings several tokens): the tensor-core kernel with 64-query tiles
+        st = core().tq_flash_prefill(
+            ptr(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width,
+            ring_pages, page_tokens, ptr(cu_seqlens), ptr(start_pos), n_seqs, T, int(window or 0), float(scale),
+            ptr(out), n_heads, n_kv_heads, head_dim, stream())
+        if st != NOT_SUPPORTED:
+            check(st, "flash_prefill")
+            return out
+    if not packed and q.dtype == torch.bfloat16 and use_flash:
         # the bandwidth-built kernel for the cache; it declines shapes outside its reach
         st = core().tq_flash_decode(
             ptr(q), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width, ring_pages, page_tokens,
