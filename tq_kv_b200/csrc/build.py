@@ -25,7 +25,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 GROUPS: dict[str, list[str]] = {
     # everything a model needs in either precision
-    "core": ["elementwise.cu", "attention.cu", "flash_decode.cu", "flash_prefill.cu", "gemm.cu", "skinny_gemm.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "attention.cu", "flash_decode.cu", "flash_prefill.cu", "gemm.cu", "skinny_gemm.cu",
+             "sampling.cu"],
+    # decode attention for callers that cannot allocate: a library of its own (flash_decode_static.h)
+    "noalloc": ["flash_decode_static.cu"],
 }
 
 NVCC_FLAGS = [
@@ -60,7 +63,9 @@ def _headers() -> list[str]:
 def group_hash(group: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for name in GROUPS[group] + _headers():
+    included = sorted(f for f in os.listdir(_HERE) if f.endswith(".cu") and f not in GROUPS[group]
+                      and any(f'#include "{f}"' in open(os.path.join(_HERE, src)).read() for src in GROUPS[group]))
+    for name in GROUPS[group] + included + _headers():
         with open(os.path.join(_HERE, name), "rb") as f:
             h.update(name.encode())
             h.update(f.read())
