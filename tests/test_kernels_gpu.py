@@ -103,8 +103,10 @@ def test_gemv_rows(M, K, dt):
 
 @pytest.mark.parametrize("M", [5, 16, 17, 300])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_linear_picks_a_kernel_for_every_shape(M, dt):
+@pytest.mark.parametrize("tcgen05", [False, True])
+def test_linear_picks_a_kernel_for_every_shape(M, dt, tcgen05, monkeypatch):
     from tq_kv_b200 import kernels
+    monkeypatch.setattr(kernels.gemm, "USE_TCGEN05", tcgen05)
     K, N = 136, 210
     x, w = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, seed=1, scale=0.1)
     want = x.double() @ w.double().T
@@ -145,6 +147,38 @@ def test_skinny_gemm(M, N, K):
     out = torch.empty(M, N, device=DEV)
     kernels.skinny_gemm(wide[:, 32:32 + K], w, out)
     close(out, wide[:, 32:32 + K].double() @ w.double().T, 1e-5 * math.sqrt(K / 64), "skinny strided")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (1, 8, 8), (2048, 512, 3584), (257, 1000, 1096)])
+def test_gemm_tc(M, N, K):
+    """The TMA + tcgen05 product: whole tiles, ragged edges in M, N and K, a long K."""
+    from tq_kv_b200 import kernels
+    x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1), rnd(N, seed=2)
+    want = x.double() @ w.double().T
+    tol = 2e-6 * math.sqrt(K)
+    out = torch.full((M, N), 7.0, device=DEV)
+    kernels.gemm_tc(x, w, out, bias)
+    kernels.check_tc_status()
+    close(out, want + bias.double(), tol, "tc store")
+    base = rnd(M, N, seed=3)
+    out = base.clone()
+    kernels.gemm_tc(x, w, out, None, kernels.gemm.EPI_ACCUM)
+    close(out, base.double() + want, tol, "tc accumulate")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc(x, w, out)
+    close(out, want, 4e-3, "tc bf16 out")
+    if N % 2 == 0:
+        w2 = rnd(2 * N, K, dtype=torch.bfloat16, seed=4, scale=2.0 / math.sqrt(K))
+        y = x.double() @ w2.double().T
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tc(x, w2, out, None, kernels.gemm.EPI_SWIGLU)
+        close(out, torch.nn.functional.silu(y[:, :N]) * y[:, N:], 4e-3, "tc swiglu")
+    # operands that are views with a row stride
+    wide = rnd(M, K + 64, dtype=torch.bfloat16, seed=6)
+    out = torch.empty(M, N, device=DEV)
+    kernels.gemm_tc(wide[:, 32:32 + K], w, out)
+    close(out, wide[:, 32:32 + K].double() @ w.double().T, tol, "tc strided")
+    kernels.check_tc_status()
 
 
 # ---- rotary encoding and cache append ----------------------------------------------

@@ -16,6 +16,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from .. import kernels
 from ..cache import PAGE_TOKENS, CacheError, SequenceCache
 from ..config import read_config_json, spec_from_config_dict
 from ..parts import Runtime
@@ -168,6 +169,7 @@ class Engine:
                 batch = build_step_batch(rows, self.cache, self.runtime.device)
                 logits = self.model.forward(batch, self.cache)
                 self.h2d_bytes += batch.packed_bytes
+                kernels.check_tc_status()      # a tensor-core product that gave up on a wait must not pass silently
         self.cache.commit(slots, lens)
         self.steps_run += 1
         return logits

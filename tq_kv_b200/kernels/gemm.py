@@ -6,9 +6,11 @@
     SwiGLU gating and the float32 accumulation into the residual stream;
   * up to 16 rows of anything else: the float32 row kernel of csrc/gemm.cu
     with the same epilogues;
-  * many rows, bfloat16 × bfloat16: the library matrix product (cuBLAS through
-    torch.mm with float32 output), as the reference engine does for all its
-    products (src/models/turbo_generic.rs:68-91 -> candle -> cuBLAS);
+  * many rows, bfloat16 × bfloat16: the TMA + tcgen05 kernel of
+    csrc/gemm_tc.cu with the same fused epilogues; with USE_TCGEN05 off, the
+    library matrix product (cuBLAS through torch.mm with float32 output), as
+    the reference engine does for all its products
+    (src/models/turbo_generic.rs:68-91 -> candle -> cuBLAS);
   * everything else (the float32 path, mixed operands): the tiled float32
     FMA kernel of csrc/gemm.cu — never a reduced-precision mode.
 """
@@ -33,6 +35,52 @@ def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
     check(core().tq_skinny_gemm(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0),
                                 w.stride(0), out.stride(0), int(accumulate), int(swiglu), stream()), "skinny_gemm")
     return out
+
+
+# ---- tcgen05 + TMA product for many rows (csrc/gemm_tc.cu) -----------------------
+USE_TCGEN05 = False                 # True: csrc/gemm_tc.cu takes the many-row bfloat16 case instead of the library
+                                    # product (the library is still the faster of the two; both are tested)
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
+_tc_status: dict = {}               # device -> int32[1]; bit 1 = a pipeline wait of the kernel ran out
+_tc_launched = [0]
+
+
+def _status_for(device) -> torch.Tensor:
+    t = _tc_status.get(device)
+    if t is None:
+        t = _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE):
+    """out (=, +=) x · w^T on the tcgen05 tensor cores; with EPI_SWIGLU w holds
+    gate rows then up rows and out = silu(gate) * up.  bfloat16 operands, K a
+    multiple of 8, 16-byte aligned rows."""
+    M, K = x.shape
+    N = out.shape[1]
+    check(core().tq_gemm_tc(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0), w.stride(0),
+                            out.stride(0), epilogue, ptr(_status_for(x.device)), stream()), "gemm_tc")
+    _tc_launched[0] += 1
+    return out
+
+
+def check_tc_status() -> None:
+    """Raises if a tcgen05 product launched since the last check gave up on a
+    pipeline wait (its output is then invalid).  Synchronises with the device."""
+    if not _tc_launched[0]:
+        return
+    _tc_launched[0] = 0
+    for dev, t in _tc_status.items():
+        v = int(t.item())
+        if v:
+            t.zero_()
+            raise KernelError(f"gemm_tc on {dev}: a pipeline wait ran out (status {v}); results are invalid")
+
+
+def _tc_ok(x, w, out, swiglu) -> bool:
+    return (USE_TCGEN05 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and (not swiglu or out.shape[1] % 2 == 0) and out.dtype in (torch.float32, torch.bfloat16))
 
 
 def _skinny_ok(x, w) -> bool:
@@ -92,6 +140,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
         return skinny_gemm(x, w, out, bias, accumulate, swiglu)
     if M <= ROW_KERNEL_MAX_ROWS:
         return gemv_rows(x, w, out, bias, accumulate, swiglu)
+
+    if _tc_ok(x, w, out, swiglu) and (not accumulate or out.dtype == torch.float32):
+        return gemm_tc(x, w, out, bias, EPI_SWIGLU if swiglu else (EPI_ACCUM if accumulate else EPI_STORE))
 
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and bias is None:
         y = torch.mm(x, w.t(), out_dtype=torch.float32)          # library product, float32 out
