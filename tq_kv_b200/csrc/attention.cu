@@ -148,6 +148,8 @@ template <typename TC>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        TC* __restrict__ out, int nh, int hd, int n_splits) {
     const size_t r0 = ((size_t)blockIdx.x * nh + blockIdx.y) * n_splits;
+    pdl_wait();
+    pdl_launch();
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[2 * (r0 + s)]);
     float l = 0.f;
@@ -209,10 +211,10 @@ TQ_API int tq_attention_merge(const float* part_acc, const float* part_ml, void*
     if (n_splits < 1 || !part_acc || !part_ml) return (int)cudaErrorInvalidValue;
     const dim3 mgrid(n_tokens, nh);
     if (dtype == TQ_F32)
-        attention_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (float*)out, nh, hd, n_splits);
-    else if (dtype == TQ_BF16)
-        attention_merge_kernel<bf16><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (bf16*)out, nh, hd, n_splits);
-    else
-        return (int)cudaErrorInvalidValue;
-    return tq_launch_status();
+        return tq_launch_pdl(attention_merge_kernel<float>, mgrid, dim3(128), 0, stream, part_acc, part_ml,
+                             (float*)out, nh, hd, n_splits);
+    if (dtype == TQ_BF16)
+        return tq_launch_pdl(attention_merge_kernel<bf16>, mgrid, dim3(128), 0, stream, part_acc, part_ml,
+                             (bf16*)out, nh, hd, n_splits);
+    return (int)cudaErrorInvalidValue;
 }

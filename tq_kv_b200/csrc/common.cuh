@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define TQ_API extern "C" __attribute__((visibility("default")))
 
@@ -106,3 +107,44 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 static inline int tq_launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch -------------------------------------------
+// Kernels of a decode step are short and run back to back.  Launched with
+// this attribute, a kernel may start while its predecessor in the stream is
+// still draining: it does whatever does not depend on the predecessor (index
+// arithmetic, prefetching weights), then pdl_wait() blocks until the
+// predecessor has completed and its writes are visible.  Every kernel
+// launched this way calls pdl_wait() before it reads or writes anything a
+// predecessor may touch, and pdl_launch() right after, which lets its own
+// successor start early in turn.  Measured on the 7B decode step the overlap
+// gained 3 % at batch 1 and lost 12 % at batch 8, so it is off unless TQ_PDL=1
+// is set; without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+static inline bool tq_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("TQ_PDL");
+        on = (e && e[0] == '1') ? 1 : 0;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int tq_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = tq_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaGetLastError();
+}

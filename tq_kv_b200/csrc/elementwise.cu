@@ -12,6 +12,8 @@ template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int V, int* status) {
     const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch();
     const int id = tokens[t];
     float* o = out + (size_t)t * H;
     if (id < 0 || id >= V) {
@@ -28,12 +30,12 @@ TQ_API int tq_embed(const int* tokens, const void* table, int table_dtype, float
     if (n_tokens <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == TQ_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, H, V, status);
-    else if (table_dtype == TQ_BF16)
-        embed_kernel<bf16><<<n_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, out, H, V, status);
-    else
-        return (int)cudaErrorInvalidValue;
-    return tq_launch_status();
+        return tq_launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
+                             (const float*)table, out, H, V, status);
+    if (table_dtype == TQ_BF16)
+        return tq_launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
+                             (const bf16*)table, out, H, V, status);
+    return (int)cudaErrorInvalidValue;
 }
 
 // ---------------------------------------------------------------------------
@@ -47,6 +49,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ rows, int H, float eps) {
     __shared__ float red[32];
     const int r = blockIdx.x;
+    pdl_wait();
+    pdl_launch();
     const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
     TO* o = out + (size_t)r * H;
     float ss = 0.f;
@@ -80,12 +84,12 @@ TQ_API int tq_rmsnorm(const float* x, const float* w, void* out, int out_dtype, 
     if (n_rows <= 0) return 0;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (out_dtype == TQ_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, (float*)out, rows, H, eps);
-    else if (out_dtype == TQ_BF16)
-        rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, w, (bf16*)out, rows, H, eps);
-    else
-        return (int)cudaErrorInvalidValue;
-    return tq_launch_status();
+        return tq_launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, w, (float*)out, rows,
+                             H, eps);
+    if (out_dtype == TQ_BF16)
+        return tq_launch_pdl(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, w, (bf16*)out, rows, H,
+                             eps);
+    return (int)cudaErrorInvalidValue;
 }
 
 // ---------------------------------------------------------------------------
@@ -113,6 +117,8 @@ __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* _
                                       TC* __restrict__ v_pages, int nh, int nkv, int hd, int rot) {
     // grid (token, head): heads 0..nh-1 are q, nh..nh+nkv-1 are k, the rest are v
     const int t = blockIdx.x, head = blockIdx.y;
+    pdl_wait();
+    pdl_launch();
     const int pos = tok_pos[t];
     const int b = tok_seq[t];
     const int half = rot >> 1;
@@ -183,15 +189,15 @@ TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, c
     const int threads = hd >= 128 ? 64 : 32;
     const dim3 grid(n_tokens, nh + 2 * nkv);
 #define TQ_LAUNCH(TI, TC)                                                                                       \
-    qkv_rope_cache_kernel<TI, TC><<<grid, threads, 0, stream>>>(                                           \
-        (const TI*)qkv, bias, cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width,          \
-        ring_pages, page_tokens, (TC*)q_out, (TC*)k_out, (TC*)v_out, (TC*)k_pages, (TC*)v_pages, nh, nkv, hd, rot)
+    return tq_launch_pdl(qkv_rope_cache_kernel<TI, TC>, grid, dim3(threads), 0, stream, (const TI*)qkv, bias,  \
+                         cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width, ring_pages,   \
+                         page_tokens, (TC*)q_out, (TC*)k_out, (TC*)v_out, (TC*)k_pages, (TC*)v_pages, nh, nkv, \
+                         hd, rot)
     if (in_dtype == TQ_F32 && cache_dtype == TQ_F32) TQ_LAUNCH(float, float);
-    else if (in_dtype == TQ_F32 && cache_dtype == TQ_BF16) TQ_LAUNCH(float, bf16);
-    else if (in_dtype == TQ_BF16 && cache_dtype == TQ_BF16) TQ_LAUNCH(bf16, bf16);
-    else return (int)cudaErrorInvalidValue;
+    if (in_dtype == TQ_F32 && cache_dtype == TQ_BF16) TQ_LAUNCH(float, bf16);
+    if (in_dtype == TQ_BF16 && cache_dtype == TQ_BF16) TQ_LAUNCH(bf16, bf16);
 #undef TQ_LAUNCH
-    return tq_launch_status();
+    return (int)cudaErrorInvalidValue;
 }
 
 // ---------------------------------------------------------------------------

@@ -61,6 +61,8 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tid4 = lane & 3;
     const int n_rep = nh / nkv;
+    pdl_wait();                                            // q and this step's keys come from the predecessors
+    pdl_launch();
     const int pos = tok_pos[t];
     const int b = tok_seq[t];
     const int lo_all = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -258,10 +260,9 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
         configured = true;
     }
     const dim3 grid(n_tokens, nkv, n_splits);
-    flash_decode_kernel<HD><<<grid, FD_WARPS * 32, smem, stream>>>(
-        q, kp, vp, table, table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out, part_acc,
-        part_ml, nh, nkv, n_splits);
-    return tq_launch_status();
+    return tq_launch_pdl(flash_decode_kernel<HD>, grid, dim3(FD_WARPS * 32), smem, stream, q, kp, vp, table,
+                         table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out, part_acc,
+                         part_ml, nh, nkv, n_splits);
 }
 
 // Returns cudaErrorNotSupported (801) for shapes outside this kernel's reach

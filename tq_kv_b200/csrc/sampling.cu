@@ -83,6 +83,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     __shared__ int sh_token;
 
     const int row = blockIdx.x, tid = threadIdx.x;
+    pdl_wait();
+    pdl_launch();
     const float* lg = logits + (size_t)row * ld;
     int* cnt = counts ? counts + (size_t)row * V : nullptr;
 
@@ -248,7 +250,6 @@ TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float tempe
     if (V <= 0 || ld < V) return (int)cudaErrorInvalidValue;
     if (temperature > 0.f && !uniforms) return (int)cudaErrorInvalidValue;
     if (counts && !(penalty > 0.f)) return (int)cudaErrorInvalidValue;
-    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, uniforms, counts,
-                                                         penalty, out);
-    return tq_launch_status();
+    return tq_launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
+                         top_k, top_p, uniforms, counts, penalty, out);
 }

@@ -88,22 +88,33 @@ skinny_gemm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
     const int per = (kblocks + parts - 1) / parts;
     const int kb0 = min(kblocks, (rank * SK_WARPS + warp) * per);
     const int kb1 = min(kblocks, kb0 + per);
-    // U k-blocks per turn: all their weight loads are issued before the first mma needs one
+    // U k-blocks per turn: all their weight loads are issued before the first mma needs one.  The first
+    // turn's loads are issued before this kernel waits for its predecessor: weights do not depend on it.
     constexpr int U = (NT <= 2) ? 4 : 2;
-    for (int kb = kb0; kb < kb1; kb += U) {
-        uint4 a[U][TW][2];
-        uint4 bx[U][NT <= 2 ? NT : 1];
+    uint4 a[U][TW][2];
+    auto load_weights = [&](int kb) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const bool on = kb + u < kb1;
-            const int k = (on ? kb + u : kb) << 5;
+            const int k = (on ? kb + u : kb0) << 5;
 #pragma unroll
             for (int t = 0; t < TW; ++t) {
                 a[u][t][0] = ld_stream16(wp[t][0] + k);
                 a[u][t][1] = ld_stream16(wp[t][1] + k);
                 if (!on) a[u][t][0] = a[u][t][1] = make_uint4(0, 0, 0, 0);
             }
-            if (NT <= 2) {
+        }
+    };
+    if (kb0 < kb1) load_weights(kb0);
+    pdl_wait();                                            // the activations are ready from here on
+    pdl_launch();
+    for (int kb = kb0; kb < kb1; kb += U) {
+        if (kb > kb0) load_weights(kb);
+        uint4 bx[U][NT <= 2 ? NT : 1];
+        if (NT <= 2) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int k = (kb + u < kb1 ? kb + u : kb0) << 5;
 #pragma unroll
                 for (int n = 0; n < (NT <= 2 ? NT : 1); ++n)
                     bx[u][n] = xv[n] ? *reinterpret_cast<const uint4*>(xp[n] + k) : make_uint4(0, 0, 0, 0);
@@ -111,7 +122,7 @@ skinny_gemm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int k = (kb + u < kb1 ? kb + u : kb) << 5;
+            const int k = (kb + u < kb1 ? kb + u : kb0) << 5;
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 uint4 b;
@@ -190,13 +201,15 @@ static int launch_skinny(const bf16* X, const bf16* W, const float* bias, void* 
     cfg.blockDim = dim3(SK_WARPS * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = ranks;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;      // see pdl_wait() in the kernel
+    attr[1].val.programmaticStreamSerializationAllowed = tq_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TW, SWIGLU, TO>, X, W, bias, (TO*)Y, M, N, K, ldx,
                                        ldw, ldy, accumulate);
     if (e != cudaSuccess) return (int)e;
