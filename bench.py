@@ -116,7 +116,10 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for profiler captures)")
+    ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prefill alone (profiler captures)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiler captures)")
+    ap.add_argument("--gemm", default=None, choices=["tcgen05", "library"],
+                    help="many-row bfloat16 products: this package's tcgen05 kernel or the library (default: the package's choice)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -136,6 +139,8 @@ def main() -> int:
     from tq_kv_b200.engine import StepRow
     from tq_kv_b200.sampling import Sampler
 
+    if args.gemm is not None:
+        kernels.gemm.USE_TCGEN05 = args.gemm == "tcgen05"
     cfg = dict(tq.named_shape(args.shape))
     full_layers = cfg["num_hidden_layers"]
     n_layers = args.layers or full_layers
@@ -189,6 +194,21 @@ def main() -> int:
         for s in slots:
             engine.release(s)
         return ms, launches
+
+    if args.prefill_only:
+        T = args.prompt
+        for _ in range(2):
+            s0 = engine.new_sequence()
+            ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([StepRow(s0, ptoks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            engine.release(s0)
+        print(json.dumps({"prefill_ms": round(e0.elapsed_time(e1), 3), "tokens": T, "layers": n_layers}))
+        return 0
 
     with ClockSampler() as clocks:
         ms, launches = decode_run(args.batch, K, W)

@@ -42,6 +42,23 @@ def test_each_request_alone_and_whole(tmp_root, name, dtype):
     eng.cache.book.check()
 
 
+def test_library_products_give_the_same_as_the_tcgen05_kernel(tmp_root, monkeypatch):
+    """Many-row bfloat16 products run on this package's tcgen05 kernel; the
+    library product stays selectable and must agree."""
+    from tq_kv_b200 import kernels
+    from tq_kv_b200.engine import StepRow
+    eng, folder = engine_for(tmp_root, "b", "bfloat16")
+    toks = requests_for("b")[3]
+    outs = []
+    for own in (True, False):
+        monkeypatch.setattr(kernels.gemm, "USE_TCGEN05", own)
+        s = eng.new_sequence()
+        outs.append(eng.step([StepRow(s, toks, list(range(len(toks))))]))
+        eng.release(s)
+    assert_close(outs[0], plain_logits(folder, toks), "bfloat16", "tcgen05")
+    assert_close(outs[1], plain_logits(folder, toks), "bfloat16", "library")
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_last_32_tokens_one_by_one(tmp_root, name, dtype):
     from tq_kv_b200.engine import StepRow

@@ -3,7 +3,8 @@
 // with tcgen05.mma issued by one thread, operands brought into shared memory
 // by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a 4-stage mbarrier
 // pipeline, the accumulator in tensor memory (TMEM) and read back with
-// tcgen05.ld for the epilogue.  One block computes one 128 x 256 tile.
+// tcgen05.ld for the epilogue.  Tiles are 128 x 256; one persistent block per
+// SM walks its share of them.
 //
 // Epilogues (fused, float32): plain store (float32 or bfloat16, optional
 // bias), accumulate into a float32 C (the residual sum,
@@ -12,11 +13,13 @@
 // by the up rows, a tile's 256 accumulator columns are 128 gate columns and
 // the 128 up columns of the same outputs, and silu(gate) * up is written.
 //
-// Roles: warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the MMAs,
-// warp 2 allocates and frees TMEM, all four warps run the epilogue (warp w
-// reads TMEM lanes 32w .. 32w+31).  Every wait on an mbarrier is bounded:
-// when a bound is hit the block raises a bit in *status, stops issuing work,
-// still frees its TMEM and returns, so the host sees an error, not a hang.
+// Roles: warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the MMAs
+// (warp 1 also allocates and frees TMEM), warps 2..5 run the epilogue of one
+// accumulator while the MMAs fill the other (warp w reads TMEM lanes
+// 32 (w % 4) .. +31, transposes through shared memory and writes whole rows).
+// Every wait on an mbarrier is bounded: when a bound is hit the role raises
+// a flag, stops, the others run into their own bounds, the block still frees
+// its TMEM, raises a bit in *status and returns: an error, not a hang.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -25,11 +28,11 @@
 #define TC_BN 256
 #define TC_BK 64
 #define TC_STAGES 4
-#define TC_THREADS 128
+#define TC_THREADS 192
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_B_BYTES (TC_BN * TC_BK * 2)
 #define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
-#define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */)
+#define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 4 * 32 * 33 * 4 /* epilogue */ + 256)
 #define TC_WAIT_CYCLES (4000000000ll)     /* about two seconds of SM clock */
 
 #define EPI_STORE 0
@@ -116,7 +119,11 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t m, uint32_t n) {
 }
 
 // ---- the kernel -------------------------------------------------------------------
-// b_rows_second: SwiGLU only — row offset of the up rows in B (the number of outputs).
+// Persistent: one block per SM walks the output tiles t = blockIdx.x, + gridDim.x, ...
+// (tiles that share a B tile are neighbours, so they meet in L2).  Two
+// accumulators of 256 TMEM columns alternate, so the MMAs of a tile overlap
+// the epilogue of the tile before.  b_rows_second: SwiGLU only — row offset
+// of the up rows in B (the number of outputs).
 template <int EPI, typename TO>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -125,31 +132,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ unsigned char smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC_STAGES * TC_STAGE_BYTES);
-    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready; then the TMEM address and a failure flag
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 1);
+    float* staging = reinterpret_cast<float*>(tiles + TC_STAGES * TC_STAGE_BYTES);       // [4 warps][32][33]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 4 * 32 * 33);
+    // bars: full[S], empty[S], acc_full[2], acc_empty[2]; then the TMEM address and a failure flag
+    uint64_t* full = bars;
+    uint64_t* empty = bars + TC_STAGES;
+    uint64_t* acc_full = bars + 2 * TC_STAGES;
+    uint64_t* acc_empty = bars + 2 * TC_STAGES + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 4);
     volatile uint32_t* failed = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM;
-    // output columns of this tile; with SwiGLU a tile yields 128 outputs from 128 gate + 128 up rows of B
+    // output columns of a tile; with SwiGLU a tile yields 128 outputs from 128 gate + 128 up rows of B
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
-    const int n0 = blockIdx.x * OUT_COLS;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM;
+    const int tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
+    const int n_tiles = tiles_m * tiles_n;
     const int k_iters = (K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[TC_STAGES + s]), 1);
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
         }
-        mbar_init(smem_u32(&bars[2 * TC_STAGES]), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 4);          // one arrival per epilogue warp
+        }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    if (warp == 2) {
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TC_BN) : "memory");
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * TC_BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before();
@@ -157,130 +173,137 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0 && lane == 0) {
-        // ---- producer: TMA loads ----
-        for (int i = 0; i < k_iters; ++i) {
-            const int s = i % TC_STAGES;
-            if (!mbar_wait(smem_u32(&bars[TC_STAGES + s]), ((i / TC_STAGES) & 1) ^ 1)) { *failed = 1; break; }
-            const uint32_t full = smem_u32(&bars[s]);
-            const uint32_t a_dst = smem_u32(tiles + s * TC_STAGE_BYTES);
-            const uint32_t b_dst = a_dst + TC_A_BYTES;
-            mbar_expect_tx(full, TC_STAGE_BYTES);
-            tma_load_2d(a_dst, &map_a, i * TC_BK, m0, full);
-            if (EPI == EPI_SWIGLU) {
-                tma_load_2d(b_dst, &map_b, i * TC_BK, n0, full);                                  // 128 gate rows
-                tma_load_2d(b_dst + TC_B_BYTES / 2, &map_b, i * TC_BK, b_rows_second + n0, full); // 128 up rows
-            } else {
-                tma_load_2d(b_dst, &map_b, i * TC_BK, n0, full);
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: TMA loads ----
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * OUT_COLS;
+                for (int i = 0; i < k_iters; ++i, ++it) {
+                    const int s = it % TC_STAGES;
+                    if (!mbar_wait(smem_u32(&empty[s]), ((it / TC_STAGES) & 1) ^ 1)) { *failed = 1; ok = false; break; }
+                    const uint32_t fb = smem_u32(&full[s]);
+                    const uint32_t a_dst = smem_u32(tiles + s * TC_STAGE_BYTES);
+                    const uint32_t b_dst = a_dst + TC_A_BYTES;
+                    mbar_expect_tx(fb, TC_STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, i * TC_BK, m0, fb);
+                    if (EPI == EPI_SWIGLU) {
+                        tma_load_2d(b_dst, &map_b, i * TC_BK, n0, fb);                                  // gate rows
+                        tma_load_2d(b_dst + TC_B_BYTES / 2, &map_b, i * TC_BK, b_rows_second + n0, fb); // up rows
+                    } else {
+                        tma_load_2d(b_dst, &map_b, i * TC_BK, n0, fb);
+                    }
+                }
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ----
-        const uint32_t idesc = instr_desc(TC_BM, TC_BN);
-        bool ok = true;
-        for (int i = 0; i < k_iters && ok; ++i) {
-            const int s = i % TC_STAGES;
-            if (!mbar_wait(smem_u32(&bars[s]), (i / TC_STAGES) & 1)) { *failed = 1; ok = false; break; }
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(tiles + s * TC_STAGE_BYTES);
-            const uint32_t b_addr = a_addr + TC_A_BYTES;
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            const uint32_t idesc = instr_desc(TC_BM, TC_BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local) {
+                const uint32_t buf = local & 1;
+                if (!mbar_wait(smem_u32(&acc_empty[buf]), ((local >> 1) & 1) ^ 1)) { *failed = 1; ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                for (int i = 0; i < k_iters; ++i, ++it) {
+                    const int s = it % TC_STAGES;
+                    if (!mbar_wait(smem_u32(&full[s]), (it / TC_STAGES) & 1)) { *failed = 1; ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + s * TC_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + TC_A_BYTES;
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; ++k) {
-                // 16 elements of K = 32 bytes further inside the swizzle atom
-                tc_mma(tmem_base, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                       (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        // 16 elements of K = 32 bytes further inside the swizzle atom
+                        tc_mma(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                               (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&empty[s]));             // frees the stage when these MMAs are done
+                }
+                if (ok) tc_commit(smem_u32(&acc_full[buf]));    // this tile's accumulator is complete
             }
-            tc_commit(smem_u32(&bars[TC_STAGES + s]));          // frees the stage when these MMAs are done
         }
-        tc_commit(smem_u32(&bars[2 * TC_STAGES]));              // accumulator ready (arrives even after a failure)
+    } else {
+        // ---- epilogue warps: warp w reads TMEM lanes 32 * (w % 4) .. + 31 = rows of the tile ----
+        const int quarter = warp & 3;
+        float* st = staging + (warp - 2) * 32 * 33;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local) {
+            const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * OUT_COLS;
+            const uint32_t buf = local & 1;
+            if (!mbar_wait(smem_u32(&acc_full[buf]), (local >> 1) & 1, true)) { *failed = 1; ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC_BN;
+            const int row0 = m0 + quarter * 32;
+#pragma unroll 1
+            for (int c = 0; c < OUT_COLS; c += 32) {
+                float v[32];
+                if (EPI == EPI_SWIGLU) {
+                    float u[32];
+                    tc_ld32(t_row + c, v);
+                    tc_ld32(t_row + TC_BN / 2 + c, u);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = (v[j] / (1.f + expf(-v[j]))) * u[j];
+                } else {
+                    tc_ld32(t_row + c, v);
+                    tc_wait_ld();
+                }
+                // transpose through shared memory: thread = row  ->  thread = column, rows one after another
+#pragma unroll
+                for (int j = 0; j < 32; ++j) st[lane * 33 + j] = v[j];
+                __syncwarp();
+                const int col = n0 + c + lane;
+                const float bv = (bias && col < N) ? bias[col] : 0.f;
+                if (sizeof(TO) == 4 || EPI == EPI_ACCUM) {
+                    if (col < N) {
+                        const int rows = min(32, M - row0);
+                        TO* out = C + (size_t)row0 * ldc + col;
+                        if (EPI == EPI_ACCUM) {
+                            // all old values first (independent loads in flight), then the sums
+                            float old[32];
+#pragma unroll
+                            for (int r = 0; r < 32; ++r) old[r] = r < rows ? to_f32<TO>(out[(size_t)r * ldc]) : 0.f;
+#pragma unroll
+                            for (int r = 0; r < 32; ++r)
+                                if (r < rows) out[(size_t)r * ldc] = from_f32<TO>(st[r * 33 + lane] + bv + old[r]);
+                        } else {
+#pragma unroll 8
+                            for (int r = 0; r < rows; ++r) out[(size_t)r * ldc] = from_f32<TO>(st[r * 33 + lane] + bv);
+                        }
+                    }
+                } else {
+                    // 16-bit output: a lane writes two neighbouring columns, the warp two rows at a time
+                    const int cp = 2 * (lane & 15), half = lane >> 4;
+                    const int col2 = n0 + c + cp;
+                    const float b0 = (bias && col2 < N) ? bias[col2] : 0.f;
+                    const float b1 = (bias && col2 + 1 < N) ? bias[col2 + 1] : 0.f;
+                    for (int r = half; r < 32; r += 2) {
+                        if (row0 + r >= M) break;
+                        TO* out = C + (size_t)(row0 + r) * ldc + col2;
+                        const float x0 = st[r * 33 + cp] + b0, x1 = st[r * 33 + cp + 1] + b1;
+                        if (col2 + 1 < N && (reinterpret_cast<uintptr_t>(out) & 3) == 0) store2_f32<TO>(out, x0, x1);
+                        else {
+                            if (col2 < N) out[0] = from_f32<TO>(x0);
+                            if (col2 + 1 < N) out[1] = from_f32<TO>(x1);
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+        }
     }
     __syncwarp();
-
-    // ---- epilogue: every warp reads its 32 TMEM lanes = 32 rows of the tile ----
-    const bool acc_ok = mbar_wait(smem_u32(&bars[2 * TC_STAGES]), 0, true);
-    tc_fence_after();
-    __syncthreads();                                              // *failed is final
-    const bool good = acc_ok && *failed == 0;
-    if (good) {
-        const int row = m0 + warp * 32 + lane;
-        const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
-        if (EPI == EPI_SWIGLU) {
-#pragma unroll 1
-            for (int c = 0; c < TC_BN / 2; c += 32) {
-                float g[32], u[32];
-                tc_ld32(t_row + c, g);
-                tc_ld32(t_row + TC_BN / 2 + c, u);
-                tc_wait_ld();
-                if (row < M) {
-                    TO* out = C + (size_t)row * ldc + n0 + c;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        if (n0 + c + j + 1 < N) {
-                            const float a = (g[j] / (1.f + expf(-g[j]))) * u[j];
-                            const float b = (g[j + 1] / (1.f + expf(-g[j + 1]))) * u[j + 1];
-                            store2_f32<TO>(out + j, a, b);
-                        } else if (n0 + c + j < N) {
-                            out[j] = from_f32<TO>((g[j] / (1.f + expf(-g[j]))) * u[j]);
-                        }
-                    }
-                }
-            }
-        } else {
-#pragma unroll 1
-            for (int c = 0; c < TC_BN; c += 32) {
-                float v[32];
-                tc_ld32(t_row + c, v);
-                tc_wait_ld();
-                if (row < M) {
-                    TO* out = C + (size_t)row * ldc + n0 + c;
-                    if (bias) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + c + j < N) v[j] += bias[n0 + c + j];
-                    }
-                    const bool whole = n0 + c + 32 <= N && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-                    if (whole && sizeof(TO) == 4) {
-                        float4* o4 = reinterpret_cast<float4*>(out);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                            if (EPI == EPI_ACCUM) {
-                                const float4 old = o4[j];
-                                x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
-                            }
-                            o4[j] = x;
-                        }
-                    } else if (whole) {
-                        uint4* o4 = reinterpret_cast<uint4*>(out);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
-                            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-                            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-                            o4[j] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
-                                               *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (n0 + c + j < N) {
-                                float x = v[j];
-                                if (EPI == EPI_ACCUM) x += to_f32<TO>(out[j]);
-                                out[j] = from_f32<TO>(x);
-                            }
-                        }
-                    }
-                }
-            }
-        }
-    } else if (threadIdx.x == 0 && status) {
-        atomicOr(status, 2);                                      // a wait ran out: the result is not valid
-    }
     tc_fence_before();
     __syncthreads();
-    if (warp == 2) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)TC_BN)
+    if (threadIdx.x == 0 && *failed && status) atomicOr(status, 2);   // a wait ran out: the result is not valid
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)(2 * TC_BN))
                      : "memory");
     }
 }
@@ -309,7 +332,15 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const float* 
         configured = true;
     }
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
-    const dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (M + TC_BM - 1) / TC_BM);
+    const int n_tiles = ((N + OUT_COLS - 1) / OUT_COLS) * ((M + TC_BM - 1) / TC_BM);
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 1;
+    }
+    const int grid = n_tiles < sm_count ? n_tiles : sm_count;
     gemm_tc_kernel<EPI, TO><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(ma, mb, bias, (TO*)C, M, N, K, ldc,
                                                                         b_rows_second, status);
     return tq_launch_status();

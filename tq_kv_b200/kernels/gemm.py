@@ -38,8 +38,7 @@ def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
 
 
 # ---- tcgen05 + TMA product for many rows (csrc/gemm_tc.cu) -----------------------
-USE_TCGEN05 = False                 # True: csrc/gemm_tc.cu takes the many-row bfloat16 case instead of the library
-                                    # product (the library is still the faster of the two; both are tested)
+USE_TCGEN05 = True                  # False: the library product (cuBLAS) takes the many-row bfloat16 case
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
 _tc_status: dict = {}               # device -> int32[1]; bit 1 = a pipeline wait of the kernel ran out
 _tc_launched = [0]
