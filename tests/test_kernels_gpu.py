@@ -181,6 +181,28 @@ def test_gemm_tc(M, N, K):
     kernels.check_tc_status()
 
 
+@pytest.mark.parametrize("M", [17, 32, 33, 50, 64, 3])
+@pytest.mark.parametrize("N,K", [(37, 64), (100, 96), (512, 3584), (130, 18944), (3584, 512)])
+def test_decode_gemm_tc(M, N, K):
+    """Swapped-operand tcgen05 product for decode batches: ragged N, short and long K (cluster split-K)."""
+    from tq_kv_b200 import kernels
+    x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1), rnd(N, seed=2)
+    want = x.double() @ w.double().T
+    out = rnd(M, N, seed=3)
+    base = out.clone()
+    kernels.decode_gemm_tc(x, w, out, bias, accumulate=True)
+    close(out, base.double() + want + bias.double(), 1e-5 * math.sqrt(K / 64), "accumulate")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    kernels.decode_gemm_tc(x, w, out)
+    close(out, want, 4e-3, "bf16 out")
+    w2, b2 = rnd(2 * N, K, dtype=torch.bfloat16, seed=4, scale=2.0 / math.sqrt(K)), rnd(2 * N, seed=5)
+    y = x.double() @ w2.double().T + b2.double()
+    out = torch.empty(M, N, device=DEV)
+    kernels.decode_gemm_tc(x, w2, out, b2, swiglu=True)
+    close(out, torch.nn.functional.silu(y[:, :N]) * y[:, N:], 1e-5, "swiglu")
+    kernels.check_tc_status()
+
+
 # ---- rotary encoding and cache append ----------------------------------------------
 @pytest.mark.parametrize("cache_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 5, 48, 48), (6, 2, 80, 32), (3, 1, 16, 16)])

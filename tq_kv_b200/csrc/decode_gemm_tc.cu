@@ -1,0 +1,304 @@
+// Weight-streaming product for decoding batches of 17..64 rows on the
+// tcgen05 tensor cores, operands swapped: the 128 rows of a W tile are the
+// "M" side of the instruction, the (padded) batch is its "N" side, so the
+// accumulator D[128 weight rows x batch] sits in TMEM with one weight row per
+// lane.  Y[M,N] = X[M,K] · W[N,K]^T.
+//
+// A block owns 128 output columns (64 with SwiGLU: 64 gate rows and the 64 up
+// rows of the same outputs share a tile) and a share of K; W and X tiles come
+// in by TMA through an 8-stage mbarrier pipeline (16 KB of W per stage, so
+// ~128 KB of weights are in flight per SM).  Where 128-row tiles alone give
+// too few blocks to pull the HBM bandwidth, a thread-block cluster of 2, 4 or
+// 8 blocks splits K; the blocks then share out the tile's outputs and each
+// adds the partial sums of its share, read from all blocks' shared memory in
+// rank order (no atomics: the result does not depend on scheduling).  Epilogues as in skinny_gemm.cu: bias, SwiGLU
+// gating, adding into the float32 residual stream, float32 or bfloat16 out.
+//
+// All waits on mbarriers are bounded (see gemm_tc.cu): a wait that runs out
+// raises a bit in *status, the block still frees its TMEM and returns.
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+namespace cg = cooperative_groups;
+
+#define DG_ROWS 128                 // weight rows per tile (TMEM lanes)
+#define DG_BK 64
+#define DG_STAGES 8
+#define DG_THREADS 192
+#define DG_W_BYTES (DG_ROWS * DG_BK * 2)
+#define DG_WAIT_CYCLES (4000000000ll)
+
+__device__ __forceinline__ uint32_t dg_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool dg_wait(uint32_t bar, uint32_t parity, bool backoff = false) {
+    const long long t0 = clock64();
+    for (uint32_t i = 1;; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if (backoff) __nanosleep(200);
+        if ((i & 255u) == 0 && clock64() - t0 > DG_WAIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void dg_tma(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint64_t dg_desc(uint32_t saddr) {      // K-major tile, 128-byte swizzle (see gemm_tc.cu)
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void dg_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+
+// MP: padded batch (32 or 64) = columns of the accumulator.
+template <int MP, bool SWIGLU, typename TO>
+__global__ void __launch_bounds__(DG_THREADS, 1)
+decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                      const float* __restrict__ bias, TO* __restrict__ Y, int M, int N, int K, int ldy, int accumulate,
+                      int* __restrict__ status) {
+    constexpr int X_BYTES = MP * DG_BK * 2;
+    constexpr int STAGE_BYTES = DG_W_BYTES + X_BYTES;
+    constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
+    constexpr int RED_LD = MP + 1;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // the partial sums reuse the first stages once the pipeline has drained: [128 weight rows][MP + 1]
+    float* red = reinterpret_cast<float*>(tiles);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + DG_STAGES * STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + DG_STAGES;
+    uint64_t* acc_full = bars + 2 * DG_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * DG_STAGES + 1);
+    volatile uint32_t* failed = tmem_slot + 1;
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int n_ranks = (int)cluster.num_blocks();
+    const int rank = (int)cluster.block_rank();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x / n_ranks) * OUT_COLS;
+    const int k_total = (K + DG_BK - 1) / DG_BK;
+    const int k_per = (k_total + n_ranks - 1) / n_ranks;
+    const int k_lo = min(k_total, rank * k_per), k_hi = min(k_total, k_lo + k_per);
+    const int k_iters = k_hi - k_lo;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DG_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(dg_smem(&full[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(dg_smem(&empty[s])));
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(dg_smem(acc_full)));
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(dg_smem(tmem_slot)), "r"((uint32_t)MP) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer ----
+        for (int i = 0; i < k_iters; ++i) {
+            const int s = i % DG_STAGES;
+            if (!dg_wait(dg_smem(&empty[s]), ((i / DG_STAGES) & 1) ^ 1)) { *failed = 1; break; }
+            const uint32_t fb = dg_smem(&full[s]);
+            const uint32_t w_dst = dg_smem(tiles + s * STAGE_BYTES);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(fb), "r"((uint32_t)STAGE_BYTES)
+                         : "memory");
+            const int kc = (k_lo + i) * DG_BK;
+            if (SWIGLU) {
+                dg_tma(w_dst, &map_w, kc, n0, fb);                          // 64 gate rows
+                dg_tma(w_dst + DG_W_BYTES / 2, &map_w, kc, N + n0, fb);     // the 64 up rows of the same outputs
+            } else {
+                dg_tma(w_dst, &map_w, kc, n0, fb);
+            }
+            dg_tma(w_dst + DG_W_BYTES, &map_x, kc, 0, fb);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer: D[128 x MP] (+)= W_tile[128 x 64] · X_tile[MP x 64]^T ----
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MP >> 3) << 17) | ((uint32_t)(DG_ROWS >> 4) << 24);
+        bool ok = true;
+        for (int i = 0; i < k_iters; ++i) {
+            const int s = i % DG_STAGES;
+            if (!dg_wait(dg_smem(&full[s]), (i / DG_STAGES) & 1)) { *failed = 1; ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t w_addr = dg_smem(tiles + s * STAGE_BYTES);
+            const uint32_t x_addr = w_addr + DG_W_BYTES;
+#pragma unroll
+            for (int k = 0; k < DG_BK / 16; ++k) {
+                const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\t"
+                    "setp.ne.b32 p, %4, 0;\n\t"
+                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                    ::"r"(tmem_base), "l"(dg_desc(w_addr + k * 32)), "l"(dg_desc(x_addr + k * 32)), "r"(idesc), "r"(acc)
+                    : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                         ::"r"(dg_smem(&empty[s])) : "memory");
+        }
+        (void)ok;
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                     ::"r"(dg_smem(acc_full)) : "memory");
+    }
+    __syncwarp();
+
+    // ---- the accumulator -> shared memory (all stages are free once it is complete) ----
+    bool good = true;
+    if (warp >= 2) {
+        good = k_iters == 0 || dg_wait(dg_smem(acc_full), 0, true);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                 // weight row of this thread within the tile
+#pragma unroll
+        for (int c = 0; c < MP; c += 32) {
+            float v[32];
+            if (good && k_iters > 0) {
+                dg_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) red[row * RED_LD + c + j] = v[j];
+        }
+        if (!good) *failed = 1;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    if (n_ranks > 1) cluster.sync(); else __syncthreads();
+
+    {
+        // The (batch row, output column) pairs are dealt to the cluster's blocks in runs of 32 columns, so
+        // every block adds and writes a share; each pair's partial sums are added in rank order.
+        const float* peers[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p) peers[p] = p < n_ranks ? cluster.map_shared_rank(red, p) : red;
+        const int runs = (OUT_COLS / 32) * M;
+        for (int q = rank + n_ranks * (threadIdx.x >> 5); q < runs; q += n_ranks * (DG_THREADS / 32)) {
+            const int m = q / (OUT_COLS / 32), c = (q - m * (OUT_COLS / 32)) * 32 + lane;
+            const int col = n0 + c;
+            float pv[8], pu[8];
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {                     // all remote reads are issued before the first add
+                pv[p] = p < n_ranks ? peers[p][c * RED_LD + m] : 0.f;
+                pu[p] = (SWIGLU && p < n_ranks) ? peers[p][(c + OUT_COLS) * RED_LD + m] : 0.f;
+            }
+            float v = pv[0], u = pu[0];
+#pragma unroll
+            for (int p = 1; p < 8; ++p) { v += pv[p]; u += pu[p]; }
+            if (col >= N) continue;
+            if (bias) { v += bias[col]; if (SWIGLU) u += bias[col + N]; }
+            if (SWIGLU) v = (v / (1.f + expf(-v))) * u;
+            TO* y = Y + (size_t)m * ldy + col;
+            if (accumulate) v += to_f32<TO>(*y);
+            *y = from_f32<TO>(v);
+        }
+    }
+    if (n_ranks > 1) cluster.sync(); else __syncthreads();   // peers keep their shared memory until it was read
+    if (threadIdx.x == 0 && *failed && status) atomicOr(status, 2);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)MP)
+                     : "memory");
+    }
+}
+
+static int dg_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * 2};
+    const cuuint32_t box[2] = {DG_BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int MP, bool SWIGLU, typename TO>
+static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* Y, int M, int N, int K,
+                     int ldy, int accumulate, int* status, cudaStream_t stream) {
+    constexpr int STAGE_BYTES = DG_W_BYTES + MP * DG_BK * 2;
+    constexpr int SMEM = DG_STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(DG_ROWS * (MP + 1) * 4 <= DG_STAGES * STAGE_BYTES, "partial sums must fit in the stages");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_gemm_tc_kernel<MP, SWIGLU, TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
+    const int tiles = (N + OUT_COLS - 1) / OUT_COLS;
+    const int k_total = (K + DG_BK - 1) / DG_BK;
+    int ranks = 1;                                           // split K while the grid is small and the shares stay long
+    while (ranks < 8 && tiles * ranks < 148 && k_total / (ranks * 2) >= 6) ranks *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * ranks, 1, 1);
+    cfg.blockDim = dim3(DG_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO>, mw, mx, bias, (TO*)Y, M, N, K, ldy,
+                                       accumulate, status);
+    if (e != cudaSuccess) return (int)e;
+    return tq_launch_status();
+}
+
+// X [M <= 64, K] and W [N, K] (or [2N, K] with swiglu) bfloat16, row strides
+// ldx / ldw elements (multiples of 8, bases 16-byte aligned); Y [M, N]
+// float32 or bfloat16 (accumulate needs float32).
+TQ_API int tq_decode_gemm_tc(const void* X, const void* W, const float* bias, void* Y, int y_dtype, int M, int N, int K,
+                             int ldx, int ldw, int ldy, int accumulate, int swiglu, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7)) return (int)cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+        return (int)cudaErrorInvalidValue;
+    if (accumulate && y_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    const int mp = M <= 32 ? 32 : 64;
+    CUtensorMap mw, mx;
+    int st = dg_make_map(&mw, W, swiglu ? 2ull * N : (uint64_t)N, (uint64_t)K, (uint64_t)ldw,
+                         swiglu ? DG_ROWS / 2 : DG_ROWS);
+    if (st) return st;
+    st = dg_make_map(&mx, X, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, mp);
+    if (st) return st;
+#define TQ_DG(MP, S, T) return dg_launch<MP, S, T>(mw, mx, bias, Y, M, N, K, ldy, accumulate, status, stream)
+    if (mp == 32) {
+        if (swiglu && y_dtype == TQ_BF16) TQ_DG(32, true, bf16);
+        if (swiglu && y_dtype == TQ_F32) TQ_DG(32, true, float);
+        if (!swiglu && y_dtype == TQ_BF16) TQ_DG(32, false, bf16);
+        if (!swiglu && y_dtype == TQ_F32) TQ_DG(32, false, float);
+    } else {
+        if (swiglu && y_dtype == TQ_BF16) TQ_DG(64, true, bf16);
+        if (swiglu && y_dtype == TQ_F32) TQ_DG(64, true, float);
+        if (!swiglu && y_dtype == TQ_BF16) TQ_DG(64, false, bf16);
+        if (!swiglu && y_dtype == TQ_F32) TQ_DG(64, false, float);
+    }
+#undef TQ_DG
+    return (int)cudaErrorInvalidValue;
+}

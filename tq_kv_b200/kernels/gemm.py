@@ -1,9 +1,11 @@
 """Matrix products: y = x · W^T with W stored [out, in].
 
 `linear()` picks the kernel from the operands:
-  * up to 64 rows of bfloat16 (decoding): the weight-streaming tensor-core
+  * up to 16 rows of bfloat16 (decoding): the weight-streaming mma.sync
     kernel of csrc/skinny_gemm.cu, which reads the weight once and fuses bias,
     SwiGLU gating and the float32 accumulation into the residual stream;
+  * 17 to 64 rows of bfloat16: the same job on tcgen05 with swapped operands,
+    TMA-fed (csrc/decode_gemm_tc.cu);
   * up to 16 rows of anything else: the float32 row kernel of csrc/gemm.cu
     with the same epilogues;
   * many rows, bfloat16 × bfloat16: the TMA + tcgen05 kernel of
@@ -59,6 +61,19 @@ def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE):
     N = out.shape[1]
     check(core().tq_gemm_tc(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0), w.stride(0),
                             out.stride(0), epilogue, ptr(_status_for(x.device)), stream()), "gemm_tc")
+    _tc_launched[0] += 1
+    return out
+
+
+def decode_gemm_tc(x, w, out, bias=None, accumulate=False, swiglu=False):
+    """bfloat16 x [M <= 64, K] times w [N, K]^T on the tcgen05 tensor cores
+    with the operands swapped (csrc/decode_gemm_tc.cu): the weight streams once
+    through TMA, K is split over a thread-block cluster where tiles are few."""
+    M, K = x.shape
+    N = out.shape[1]
+    check(core().tq_decode_gemm_tc(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0),
+                                   w.stride(0), out.stride(0), int(accumulate), int(swiglu),
+                                   ptr(_status_for(x.device)), stream()), "decode_gemm_tc")
     _tc_launched[0] += 1
     return out
 
@@ -135,6 +150,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
     if M == 0:
         return out
 
+    if (USE_TCGEN05 and ROW_KERNEL_MAX_ROWS < M <= SKINNY_MAX_ROWS and _tc_ok(x, w, out, swiglu)
+            and (not accumulate or out.dtype == torch.float32)):
+        return decode_gemm_tc(x, w, out, bias, accumulate, swiglu)
     if _skinny_ok(x, w):
         return skinny_gemm(x, w, out, bias, accumulate, swiglu)
     if M <= ROW_KERNEL_MAX_ROWS:
