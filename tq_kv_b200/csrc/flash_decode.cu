@@ -18,7 +18,7 @@
 #define FD_PAGE 64           // tokens per cache page (checked by the launcher)
 
 __device__ __forceinline__ void fd_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -91,22 +91,27 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         }
     }
 
-    // issue the copy of this warp's i-th chunk into stage i % FD_STAGES: two lanes per key, half a row each
+    // issue the copy of this warp's i-th chunk into stage i % FD_STAGES.  Lane l < 16 looks up the row of
+    // key l; then consecutive lanes copy consecutive 16-byte pieces of a row, so that every 32-byte sector
+    // is asked for once.
+    constexpr int PR = HD / 8;                              // 16-byte pieces per row
     auto issue = [&](int i) {
         const int chunk = warp + i * FD_WARPS;
         if (chunk < n_chunks) {
-            int j = lo + chunk * FD_CHUNK + (lane >> 1);
-            if (j >= hi) j = hi - 1;                      // a valid address; the score is masked
+            int j = lo + chunk * FD_CHUNK + (lane & 15);
+            if (j >= hi) j = hi - 1;                       // a valid address; the score is masked
             int lp = j / FD_PAGE;
             if (ring_pages > 0) lp %= ring_pages;
-            const size_t row = (((size_t)table[lp] * nkv + g) * FD_PAGE + (j % FD_PAGE)) * HD;
-            unsigned char* ks_ = my + (i % FD_STAGES) * 2 * TILE + (lane >> 1) * ROW;
+            const unsigned long long my_row = (((unsigned long long)table[lp] * nkv + g) * FD_PAGE + (j % FD_PAGE)) * HD;
+            unsigned char* ks_ = my + (i % FD_STAGES) * 2 * TILE;
             unsigned char* vs_ = ks_ + TILE;
-            const int c0 = (lane & 1) * (HD / 16);
 #pragma unroll
-            for (int c = 0; c < HD / 16; ++c) {
-                fd_cp_async16(ks_ + (c0 + c) * 16, k_pages + row + (c0 + c) * 8);
-                fd_cp_async16(vs_ + (c0 + c) * 16, v_pages + row + (c0 + c) * 8);
+            for (int it = 0; it < PR / 2; ++it) {
+                const int p = lane + 32 * it;
+                const int key = p / PR, c = p - key * PR;
+                const unsigned long long row = __shfl_sync(0xffffffffu, my_row, key);
+                fd_cp_async16(ks_ + key * ROW + c * 16, k_pages + row + c * 8);
+                fd_cp_async16(vs_ + key * ROW + c * 16, v_pages + row + c * 8);
             }
         }
         fd_commit();                                       // one group per turn, empty or not
