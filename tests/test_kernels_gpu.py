@@ -141,7 +141,7 @@ def test_skinny_gemm(M, N, K):
     y = x.double() @ w2.double().T + b2.double()
     out = torch.empty(M, N, device=DEV)
     kernels.skinny_gemm(x, w2, out, b2, swiglu=True)
-    close(out, torch.nn.functional.silu(y[:, :N]) * y[:, N:], 1e-5, "skinny swiglu")
+    close(out, torch.nn.functional.silu(y[:, :N]) * y[:, N:], 1e-5 * math.sqrt(K / 64), "skinny swiglu")
     # a view with a row stride (columns of a wider matrix)
     wide = rnd(M, K + 64, dtype=torch.bfloat16, seed=6)
     out = torch.empty(M, N, device=DEV)
@@ -199,7 +199,8 @@ def test_decode_gemm_tc(M, N, K):
     y = x.double() @ w2.double().T + b2.double()
     out = torch.empty(M, N, device=DEV)
     kernels.decode_gemm_tc(x, w2, out, b2, swiglu=True)
-    close(out, torch.nn.functional.silu(y[:, :N]) * y[:, N:], 1e-5, "swiglu")
+    # float32 accumulation over K terms: the rounding error grows with sqrt(K), as in the check above
+    close(out, torch.nn.functional.silu(y[:, :N]) * y[:, N:], 1e-5 * math.sqrt(K / 64), "swiglu")
     kernels.check_tc_status()
 
 

@@ -6,8 +6,9 @@
 //
 // A block owns 128 output columns (64 with SwiGLU: 64 gate rows and the 64 up
 // rows of the same outputs share a tile) and a share of K; W and X tiles come
-// in by TMA through an 8-stage mbarrier pipeline (16 KB of W per stage, so
-// ~128 KB of weights are in flight per SM).  Where 128-row tiles alone give
+// in by TMA through a 4-stage mbarrier pipeline (16 KB of W per stage; two
+// blocks fit an SM, so ~128 KB of weights are in flight per SM and one
+// block's epilogue runs under the other's loads).  Where 128-row tiles alone give
 // too few blocks to pull the HBM bandwidth, a thread-block cluster of 2, 4 or
 // 8 blocks splits K; the blocks then share out the tile's outputs and each
 // adds the partial sums of its share, read from all blocks' shared memory in
@@ -24,7 +25,7 @@ namespace cg = cooperative_groups;
 
 #define DG_ROWS 128                 // weight rows per tile (TMEM lanes)
 #define DG_BK 64
-#define DG_STAGES 8
+#define DG_STAGES 4                 // 96 KB per block: two blocks per SM, one's epilogue under the other's loads
 #define DG_THREADS 192
 #define DG_W_BYTES (DG_ROWS * DG_BK * 2)
 #define DG_WAIT_CYCLES (4000000000ll)
@@ -67,7 +68,7 @@ __device__ __forceinline__ void dg_ld32(uint32_t taddr, float* v) {
 
 // MP: padded batch (32 or 64) = columns of the accumulator.
 template <int MP, bool SWIGLU, typename TO>
-__global__ void __launch_bounds__(DG_THREADS, 1)
+__global__ void __launch_bounds__(DG_THREADS, 2)
 decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       const float* __restrict__ bias, TO* __restrict__ Y, int M, int N, int K, int ldy, int accumulate,
                       int* __restrict__ status) {
@@ -223,6 +224,9 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
 }
 
+static int g_force_ranks = 0;       // tuning aid: a fixed cluster size instead of the heuristic (0 = heuristic)
+TQ_API void tq_decode_gemm_tc_force_ranks(int ranks) { g_force_ranks = ranks; }
+
 static int dg_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {ld * 2};
@@ -250,8 +254,10 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
     constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
     const int tiles = (N + OUT_COLS - 1) / OUT_COLS;
     const int k_total = (K + DG_BK - 1) / DG_BK;
-    int ranks = 1;                                           // split K while the grid is small and the shares stay long
-    while (ranks < 8 && tiles * ranks < 148 && k_total / (ranks * 2) >= 6) ranks *= 2;
+    // split K while the grid is small and the shares stay long (measured best on the 7B shapes: 2 to 4 blocks)
+    int ranks = 1;
+    while (ranks < 4 && tiles * ranks < 64 && k_total / (ranks * 2) >= 4) ranks *= 2;
+    if (g_force_ranks > 0) ranks = g_force_ranks;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * ranks, 1, 1);
     cfg.blockDim = dim3(DG_THREADS, 1, 1);

@@ -27,6 +27,7 @@ from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, st
 
 ROW_KERNEL_MAX_ROWS = 16
 SKINNY_MAX_ROWS = 64
+TC_DECODE_MIN_WEIGHT_BYTES = 64 << 20
 
 
 def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
@@ -150,8 +151,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
     if M == 0:
         return out
 
-    if (USE_TCGEN05 and ROW_KERNEL_MAX_ROWS < M <= SKINNY_MAX_ROWS and _tc_ok(x, w, out, swiglu)
-            and (not accumulate or out.dtype == torch.float32)):
+    # decoding: the TMA-fed tcgen05 kernel for batches over 16 rows and for large weights at any batch (measured
+    # faster from about 64 MB of weight on), the mma.sync kernel for small weights at small batches
+    if (USE_TCGEN05 and M <= SKINNY_MAX_ROWS and _tc_ok(x, w, out, swiglu)
+            and (not accumulate or out.dtype == torch.float32)
+            and (M > ROW_KERNEL_MAX_ROWS or w.numel() * 2 >= TC_DECODE_MIN_WEIGHT_BYTES or not _skinny_ok(x, w))):
         return decode_gemm_tc(x, w, out, bias, accumulate, swiglu)
     if _skinny_ok(x, w):
         return skinny_gemm(x, w, out, bias, accumulate, swiglu)
