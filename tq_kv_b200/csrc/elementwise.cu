@@ -176,6 +176,90 @@ __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* _
     }
 }
 
+// The same for the common serving case (float32 in, bfloat16 out, the whole head rotated, head_dim a
+// multiple of 8): one block per token, every thread handles four neighbouring dims with 16-byte loads.
+__device__ __forceinline__ uint2 pack4_bf16(float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    return make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
+__global__ void __launch_bounds__(256)
+qkv_rope_cache_vec_kernel(const float* __restrict__ qkv, const float* __restrict__ bias,
+                          const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                          const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                          const int* __restrict__ new_lens, const int* __restrict__ block_table, int table_width,
+                          int ring_pages, int page_tokens, bf16* __restrict__ q_out, bf16* __restrict__ k_out,
+                          bf16* __restrict__ v_out, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int nh,
+                          int nkv, int hd) {
+    const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch();
+    const int pos = tok_pos[t];
+    const int b = tok_seq[t];
+    const int half = hd >> 1, q4 = half >> 2;
+    const float* x = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+    const float* cs = cos_tab + (size_t)pos * half;
+    const float* sn = sin_tab + (size_t)pos * half;
+    size_t cache_row = 0;
+    bool to_cache = k_pages != nullptr;
+    if (to_cache) {
+        int lp = pos / page_tokens;
+        if (ring_pages > 0) {
+            if (pos < new_lens[b] - ring_pages * page_tokens) to_cache = false;
+            lp %= ring_pages;
+        }
+        if (to_cache)
+            cache_row = ((size_t)block_table[(size_t)b * table_width + lp] * nkv) * page_tokens + (pos % page_tokens);
+    }
+    for (int idx = threadIdx.x; idx < (nh + nkv) * q4; idx += blockDim.x) {
+        const int head = idx / q4, j = (idx - head * q4) * 4;
+        const int c0 = head * hd + j;
+        float4 x0 = *reinterpret_cast<const float4*>(x + c0);
+        float4 x1 = *reinterpret_cast<const float4*>(x + c0 + half);
+        if (bias) {
+            const float4 b0 = *reinterpret_cast<const float4*>(bias + c0);
+            const float4 b1 = *reinterpret_cast<const float4*>(bias + c0 + half);
+            x0.x += b0.x; x0.y += b0.y; x0.z += b0.z; x0.w += b0.w;
+            x1.x += b1.x; x1.y += b1.y; x1.z += b1.z; x1.w += b1.w;
+        }
+        const float4 c = *reinterpret_cast<const float4*>(cs + j);
+        const float4 s = *reinterpret_cast<const float4*>(sn + j);
+        const uint2 r0 = pack4_bf16(x0.x * c.x - x1.x * s.x, x0.y * c.y - x1.y * s.y, x0.z * c.z - x1.z * s.z,
+                                    x0.w * c.w - x1.w * s.w);
+        const uint2 r1 = pack4_bf16(x0.x * s.x + x1.x * c.x, x0.y * s.y + x1.y * c.y, x0.z * s.z + x1.z * c.z,
+                                    x0.w * s.w + x1.w * c.w);
+        if (head < nh) {
+            bf16* q = q_out + ((size_t)t * nh + head) * hd + j;
+            *reinterpret_cast<uint2*>(q) = r0;
+            *reinterpret_cast<uint2*>(q + half) = r1;
+        } else {
+            const int g = head - nh;
+            if (k_out) {
+                bf16* k = k_out + ((size_t)t * nkv + g) * hd + j;
+                *reinterpret_cast<uint2*>(k) = r0;
+                *reinterpret_cast<uint2*>(k + half) = r1;
+            }
+            if (to_cache) {
+                bf16* k = k_pages + (cache_row + (size_t)g * page_tokens) * hd + j;
+                *reinterpret_cast<uint2*>(k) = r0;
+                *reinterpret_cast<uint2*>(k + half) = r1;
+            }
+        }
+    }
+    const int v0 = (nh + nkv) * hd;
+    for (int idx = threadIdx.x; idx < nkv * (hd >> 2); idx += blockDim.x) {
+        const int g = idx / (hd >> 2), d = (idx - g * (hd >> 2)) * 4;
+        float4 v = *reinterpret_cast<const float4*>(x + v0 + g * hd + d);
+        if (bias) {
+            const float4 bv = *reinterpret_cast<const float4*>(bias + v0 + g * hd + d);
+            v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+        }
+        const uint2 r = pack4_bf16(v.x, v.y, v.z, v.w);
+        if (v_out) *reinterpret_cast<uint2*>(v_out + ((size_t)t * nkv + g) * hd + d) = r;
+        if (to_cache) *reinterpret_cast<uint2*>(v_pages + (cache_row + (size_t)g * page_tokens) * hd + d) = r;
+    }
+}
+
 TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, const float* cos_tab,
                              const float* sin_tab, const int* tok_pos, const int* tok_seq, const int* new_lens,
                              const int* block_table, int table_width, int ring_pages, int page_tokens, void* q_out,
@@ -186,6 +270,12 @@ TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, c
     if ((k_pages == nullptr) != (v_pages == nullptr)) return (int)cudaErrorInvalidValue;
     if (k_pages && !block_table) return (int)cudaErrorInvalidValue;
     if (nh + 2 * nkv > 65535) return (int)cudaErrorInvalidValue;
+    if (in_dtype == TQ_F32 && cache_dtype == TQ_BF16 && rot == hd && (hd & 7) == 0 &&
+        (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0))
+        return tq_launch_pdl(qkv_rope_cache_vec_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)qkv,
+                             bias, cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width,
+                             ring_pages, page_tokens, (bf16*)q_out, (bf16*)k_out, (bf16*)v_out, (bf16*)k_pages,
+                             (bf16*)v_pages, nh, nkv, hd);
     const int threads = hd >= 128 ? 64 : 32;
     const dim3 grid(n_tokens, nh + 2 * nkv);
 #define TQ_LAUNCH(TI, TC)                                                                                       \

@@ -241,15 +241,62 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     }
 }
 
+// Arg-max in two steps for speed: the vocabulary of a row is cut into ARGMAX_PARTS parts, one block each;
+// a second kernel picks the best part (lowest id on ties) and counts the chosen token.
+#define ARGMAX_PARTS 32
+
+__global__ void __launch_bounds__(256)
+argmax_parts_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ counts, float penalty,
+                    ArgMax* __restrict__ parts) {
+    __shared__ ArgMax red[32];
+    const int row = blockIdx.x, part = blockIdx.y;
+    pdl_wait();
+    pdl_launch();
+    const float* lg = logits + (size_t)row * ld;
+    const int* cnt = counts ? counts + (size_t)row * V : nullptr;
+    const int per = (V + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+    const int lo = part * per, hi = min(V, lo + per);
+    ArgMax am{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) am = better(am, ArgMax{penalised(lg, cnt, penalty, i), i});
+    am = block_argmax(am, red);
+    if (threadIdx.x == 0) parts[row * ARGMAX_PARTS + part] = am;
+}
+
+__global__ void argmax_final_kernel(const ArgMax* __restrict__ parts, int* __restrict__ counts, int V,
+                                    int* __restrict__ out) {
+    const int row = blockIdx.x, lane = threadIdx.x;
+    pdl_wait();
+    pdl_launch();
+    ArgMax a = lane < ARGMAX_PARTS ? parts[row * ARGMAX_PARTS + lane] : ArgMax{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax b{__shfl_xor_sync(0xffffffffu, a.v, o), __shfl_xor_sync(0xffffffffu, a.i, o)};
+        a = better(a, b);
+    }
+    if (lane == 0) {
+        out[row] = a.i;
+        if (counts) counts[(size_t)row * V + a.i] += 1;
+    }
+}
+
 // counts: int32 [rows, V] occurrence counts of generated tokens (or null);
 // the sampled token's count is incremented.  uniforms: float [rows] in [0, 1)
 // (unused when temperature <= 0).
+// scratch: optional, 8 * 32 bytes per row; with it, arg-max runs as two short kernels on many blocks.
 TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float temperature, int top_k, float top_p,
-                     const float* uniforms, int* counts, float penalty, int* out, cudaStream_t stream) {
+                     const float* uniforms, int* counts, float penalty, int* out, void* scratch,
+                     cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V) return (int)cudaErrorInvalidValue;
     if (temperature > 0.f && !uniforms) return (int)cudaErrorInvalidValue;
     if (counts && !(penalty > 0.f)) return (int)cudaErrorInvalidValue;
+    if (temperature <= 0.f && scratch && n_rows <= 65535) {
+        int st = tq_launch_pdl(argmax_parts_kernel, dim3(n_rows, ARGMAX_PARTS), dim3(256), 0, stream, logits, ld, V,
+                               (const int*)counts, penalty, (ArgMax*)scratch);
+        if (st) return st;
+        return tq_launch_pdl(argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, (const ArgMax*)scratch, counts, V,
+                             out);
+    }
     return tq_launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
                          top_k, top_p, uniforms, counts, penalty, out);
 }

@@ -80,7 +80,7 @@ _SIGNATURES = {
                          c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "tq_attention_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p,
-                  c_void_p],
+                  c_void_p, c_void_p],
 }
 
 _core = None

@@ -27,6 +27,21 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float = 0.0,
     if counts is not None and (counts.dtype != torch.int32 or tuple(counts.shape) != (R, V)):
         raise KernelError("sample: counts must be int32 [R, V]")
     need_contiguous(out=out, uniforms=uniforms, counts=counts)
+    scratch = None
+    if temperature <= 0:
+        scratch = _argmax_scratch(logits.device, R)
     check(core().tq_sample(ptr(logits), logits.stride(0), R, V, float(temperature), int(top_k), float(top_p),
-                           ptr(uniforms), ptr(counts), float(repeat_penalty), ptr(out), stream()), "sample")
+                           ptr(uniforms), ptr(counts), float(repeat_penalty), ptr(out), ptr(scratch), stream()),
+          "sample", 2 if scratch is not None else 1)
     return out
+
+
+_scratch: dict = {}
+
+
+def _argmax_scratch(device, rows: int) -> torch.Tensor:
+    """(value, index) pairs of the arg-max's first step: 32 per row, kept per device and grown on demand."""
+    t = _scratch.get(device)
+    if t is None or t.numel() < rows * 64:
+        t = _scratch[device] = torch.empty(max(rows, 64) * 64, dtype=torch.int32, device=device)
+    return t
