@@ -1,0 +1,58 @@
+"""Layers of the sizes of Qwen2.5-0.5B, 7B and 32B (a few layers, a small
+vocabulary, random weights) against the plain implementation: the kernels'
+fast paths are picked by head size, group size and widths, and these are the
+sizes they will meet (GPU)."""
+import os
+
+import pytest
+import torch
+
+from helpers import assert_close, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+# name of the shape, layers kept, tokens fed
+SHAPES = [("qwen2.5-0.5b", 2, 150), ("qwen2.5-7b", 2, 150), ("qwen2.5-32b", 1, 90)]
+VOCAB = 3000        # the vocabulary is cut down: the embedding and head matrices of 152k rows only cost time here
+
+
+@pytest.fixture(scope="module")
+def tmp_root(tmp_path_factory):
+    return tmp_path_factory.mktemp("real")
+
+
+@pytest.mark.parametrize("shape,layers,n_tokens", SHAPES)
+def test_real_layer_sizes_whole_then_decoded_and_batched(tmp_root, shape, layers, n_tokens):
+    import tq_kv_b200 as tq
+    from tq_kv_b200.engine import Engine, StepRow
+    from tq_kv_b200.weights import write_model_folder
+    cfg = dict(tq.named_shape(shape))
+    cfg.update(num_hidden_layers=layers, max_window_layers=layers, vocab_size=VOCAB, torch_dtype="bfloat16",
+               max_position_embeddings=1024)
+    folder = write_model_folder(cfg, os.path.join(str(tmp_root), shape), seed=8, device="cuda")
+    reqs = [random_tokens(n_tokens, VOCAB, 300 + i) for i in range(2)]
+    reqs[1] = reqs[1][:n_tokens // 2 + 3]
+    wants = [plain_logits(folder, r) for r in reqs]
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=512)
+        # whole
+        s = eng.new_sequence()
+        got = eng.step([StepRow(s, reqs[0], list(range(n_tokens)))])
+        eng.release(s)
+        assert_close(got, wants[0], dtype, f"{shape} whole")
+        # an unequal batch: prompts, then one token each until the shorter one ends, then the longer one alone
+        slots = [eng.new_sequence(), eng.new_sequence()]
+        cut = [len(reqs[0]) - 20, len(reqs[1]) - 12]
+        got = eng.step([StepRow(slots[i], reqs[i][:cut[i]], [cut[i] - 1]) for i in range(2)])
+        assert_close(got, torch.stack([wants[i][cut[i] - 1] for i in range(2)]), dtype, f"{shape} prompts")
+        live = [0, 1]
+        while live:
+            got = eng.step([StepRow(slots[i], [reqs[i][cut[i]]], [0]) for i in live])
+            assert_close(got, torch.stack([wants[i][cut[i]] for i in live]), dtype, f"{shape} decode")
+            for i in list(live):
+                cut[i] += 1
+                if cut[i] == len(reqs[i]):
+                    eng.release(slots[i])
+                    live.remove(i)
+        del eng
+        torch.cuda.empty_cache()
