@@ -209,17 +209,18 @@ def test_decode_gemm_tc(M, N, K):
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 5, 48, 48), (6, 2, 80, 32), (3, 1, 16, 16)])
 def test_qkv_rope_cache(cache_dtype, nh, nkv, hd, rot):
     from tq_kv_b200 import kernels
-    lens, starts = [70, 3, 1], [0, 130, 64]            # row 0: a prompt; rows 1, 2: continuations
+    lens, starts = [70 + 128, 3, 1], [0, 130, 64]      # row 0: a prompt; rows 1, 2: continuations
     T, B = sum(lens), 3
     width = (nh + 2 * nkv) * hd
     qkv, bias = rnd(T, width), rnd(width, seed=1)
     cos, sin = pm.rope_tables(rot, 50000.0, 256)
+    # (over 128 tokens, so that the 16-byte kernel for many tokens runs where its conditions hold)
     tok_seq = torch.tensor(sum(([b] * n for b, n in enumerate(lens)), []), dtype=torch.int32, device=DEV)
     pos = sum((list(range(s, s + n)) for s, n in zip(starts, lens)), [])
     tok_pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
     new_lens = torch.tensor([s + n for s, n in zip(starts, lens)], dtype=torch.int32, device=DEV)
-    pages, P = 9, 64
-    table = torch.tensor([[4, 7, 0], [1, 8, 2], [3, 5, 6]], dtype=torch.int32, device=DEV)
+    pages, P = 10, 64
+    table = torch.tensor([[4, 7, 0, 9], [1, 8, 2, 9], [3, 5, 6, 9]], dtype=torch.int32, device=DEV)
     kp = torch.zeros(pages, nkv, P, hd, dtype=cache_dtype, device=DEV)
     vp = torch.zeros_like(kp)
     q = torch.empty(T, nh * hd, dtype=cache_dtype, device=DEV)
@@ -227,7 +228,7 @@ def test_qkv_rope_cache(cache_dtype, nh, nkv, hd, rot):
     v = torch.empty_like(k)
     kernels.qkv_rope_cache(qkv, bias, cos.to(DEV), sin.to(DEV), tok_pos, tok_seq, new_lens, q, n_heads=nh,
                            n_kv_heads=nkv, head_dim=hd, rotary_dim=rot, k_out=k, v_out=v, k_pages=kp, v_pages=vp,
-                           block_table=table, table_width=3, ring_pages=0, page_tokens=P)
+                           block_table=table, table_width=4, ring_pages=0, page_tokens=P)
     x = (qkv + bias).cpu()
     xq = x[:, :nh * hd].reshape(T, nh, hd)
     xk = x[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd)

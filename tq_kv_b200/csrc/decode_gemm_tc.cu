@@ -25,7 +25,6 @@ namespace cg = cooperative_groups;
 
 #define DG_ROWS 128                 // weight rows per tile (TMEM lanes)
 #define DG_BK 64
-#define DG_STAGES 4                 // 96 KB per block: two blocks per SM, one's epilogue under the other's loads
 #define DG_THREADS 192
 #define DG_W_BYTES (DG_ROWS * DG_BK * 2)
 #define DG_WAIT_CYCLES (4000000000ll)
@@ -67,8 +66,9 @@ __device__ __forceinline__ void dg_ld32(uint32_t taddr, float* v) {
 }
 
 // MP: padded batch (32 or 64) = columns of the accumulator.
-template <int MP, bool SWIGLU, typename TO>
-__global__ void __launch_bounds__(DG_THREADS, 2)
+// DG_STAGES: 4 (96 KB per block: two blocks fit an SM, one's epilogue runs under the other's loads) or 8.
+template <int MP, bool SWIGLU, typename TO, int DG_STAGES>
+__global__ void __launch_bounds__(DG_THREADS, DG_STAGES == 4 ? 2 : 1)
 decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       const float* __restrict__ bias, TO* __restrict__ Y, int M, int N, int K, int ldy, int accumulate,
                       int* __restrict__ status) {
@@ -224,9 +224,6 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
 }
 
-static int g_force_ranks = 0;       // tuning aid: a fixed cluster size instead of the heuristic (0 = heuristic)
-TQ_API void tq_decode_gemm_tc_force_ranks(int ranks) { g_force_ranks = ranks; }
-
 static int dg_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {ld * 2};
@@ -238,26 +235,25 @@ static int dg_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
-template <int MP, bool SWIGLU, typename TO>
-static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* Y, int M, int N, int K,
-                     int ldy, int accumulate, int* status, cudaStream_t stream) {
+static int g_force_ranks = 0;       // tuning aids: fixed cluster size / stage count instead of the heuristics
+static int g_force_stages = 0;
+TQ_API void tq_decode_gemm_tc_force(int ranks, int stages) { g_force_ranks = ranks; g_force_stages = stages; }
+
+template <int MP, bool SWIGLU, typename TO, int DG_STAGES>
+static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* Y, int M, int N, int K,
+                       int ldy, int accumulate, int* status, int ranks, cudaStream_t stream) {
     constexpr int STAGE_BYTES = DG_W_BYTES + MP * DG_BK * 2;
     constexpr int SMEM = DG_STAGES * STAGE_BYTES + 1024 + 256;
     static_assert(DG_ROWS * (MP + 1) * 4 <= DG_STAGES * STAGE_BYTES, "partial sums must fit in the stages");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_gemm_tc_kernel<MP, SWIGLU, TO>,
+        cudaError_t e = cudaFuncSetAttribute(decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
     const int tiles = (N + OUT_COLS - 1) / OUT_COLS;
-    const int k_total = (K + DG_BK - 1) / DG_BK;
-    // split K while the grid is small and the shares stay long (measured best on the 7B shapes: 2 to 4 blocks)
-    int ranks = 1;
-    while (ranks < 4 && tiles * ranks < 64 && k_total / (ranks * 2) >= 4) ranks *= 2;
-    if (g_force_ranks > 0) ranks = g_force_ranks;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * ranks, 1, 1);
     cfg.blockDim = dim3(DG_THREADS, 1, 1);
@@ -270,10 +266,28 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO>, mw, mx, bias, (TO*)Y, M, N, K, ldy,
-                                       accumulate, status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES>, mw, mx, bias, (TO*)Y, M,
+                                       N, K, ldy, accumulate, status);
     if (e != cudaSuccess) return (int)e;
     return tq_launch_status();
+}
+
+template <int MP, bool SWIGLU, typename TO>
+static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* Y, int M, int N, int K,
+                     int ldy, int accumulate, int* status, cudaStream_t stream) {
+    constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
+    const int tiles = (N + OUT_COLS - 1) / OUT_COLS;
+    const int k_total = (K + DG_BK - 1) / DG_BK;
+    // split K while the grid is small and the shares stay long.  Measured best on the 7B shapes: up to 4
+    // blocks and about 64 blocks in all for batches over 16 rows, up to 8 and a full GPU for smaller ones.
+    const int max_ranks = M > 16 ? 4 : 8, want_blocks = M > 16 ? 64 : 148;
+    int ranks = 1;
+    while (ranks < max_ranks && tiles * ranks < want_blocks && k_total / (ranks * 2) >= 4) ranks *= 2;
+    if (g_force_ranks > 0) ranks = g_force_ranks;
+    int stages = 4;
+    if (g_force_stages > 0) stages = g_force_stages;
+    if (stages == 8) return dg_launch_s<MP, SWIGLU, TO, 8>(mw, mx, bias, Y, M, N, K, ldy, accumulate, status, ranks, stream);
+    return dg_launch_s<MP, SWIGLU, TO, 4>(mw, mx, bias, Y, M, N, K, ldy, accumulate, status, ranks, stream);
 }
 
 // X [M <= 64, K] and W [N, K] (or [2N, K] with swiglu) bfloat16, row strides

@@ -270,7 +270,8 @@ TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, c
     if ((k_pages == nullptr) != (v_pages == nullptr)) return (int)cudaErrorInvalidValue;
     if (k_pages && !block_table) return (int)cudaErrorInvalidValue;
     if (nh + 2 * nkv > 65535) return (int)cudaErrorInvalidValue;
-    if (in_dtype == TQ_F32 && cache_dtype == TQ_BF16 && rot == hd && (hd & 7) == 0 &&
+    // many tokens: one block per token with 16-byte accesses; few tokens (decoding): one block per (token, head)
+    if (n_tokens >= 128 && in_dtype == TQ_F32 && cache_dtype == TQ_BF16 && rot == hd && (hd & 7) == 0 &&
         (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0))
         return tq_launch_pdl(qkv_rope_cache_vec_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)qkv,
                              bias, cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width,
