@@ -164,19 +164,32 @@ flash_prefill_kernel(const bf16* __restrict__ q, FpSource src, const int* __rest
                 fp_mma(s[n + 1], qf[ks], kb[2], kb[3]);
             }
         }
-        // scale and mask: key j is seen by the row at position p iff p - window < j <= p
+        // scale and mask: key j is seen by the row at position p iff p - window < j <= p.  Most tiles lie
+        // wholly inside every row's range (the same answer for the whole block): they skip the tests.
         float mx[2] = {-INFINITY, -INFINITY};
+        const bool inside = j0 + FP_BN - 1 <= p_first && (window <= 0 || j0 > p_last - window);
+        if (inside) {
 #pragma unroll
-        for (int n = 0; n < FP_BN / 8; ++n)
+            for (int n = 0; n < FP_BN / 8; ++n)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = j0 + n * 8 + 2 * tid4 + (e & 1);
-                const int p = rp[e >> 1];
-                const bool seen = j <= p && (window <= 0 || j > p - window);
-                const float v = seen ? s[n][e] * scale_log2 : -INFINITY;
-                s[n][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    const float v = s[n][e] * scale_log2;
+                    s[n][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+        } else {
+#pragma unroll
+            for (int n = 0; n < FP_BN / 8; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + n * 8 + 2 * tid4 + (e & 1);
+                    const int p = rp[e >> 1];
+                    const bool seen = j <= p && (window <= 0 || j > p - window);
+                    const float v = seen ? s[n][e] * scale_log2 : -INFINITY;
+                    s[n][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+        }
         float corr[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
