@@ -68,6 +68,7 @@ class GQAttention(Mixer):
             self.b_qkv = torch.cat([float32_vector(tensors[self._n(x, "bias")]) for x in "qkv"]).contiguous()
         if self.out_bias:
             self.b_o = float32_vector(tensors[self._n("o", "bias")])
+        self.position.bind(tensors, runtime, shared)      # a position encoding may have tensors of its own
         self.position.prepare(runtime, shared)
 
     # ---- cache ------------------------------------------------------------
