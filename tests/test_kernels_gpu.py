@@ -204,6 +204,20 @@ def test_decode_gemm_tc(M, N, K):
     kernels.check_tc_status()
 
 
+def test_gemm_tc_accumulate_with_a_short_last_round():
+    """More tiles than SMs with a remainder: the residual product cuts the last round's tiles along K and the
+    shares add up in C (16 x 14 = 224 tiles of 128 x 256, as o_proj at 2,048 tokens of the 7B shape)."""
+    from tq_kv_b200 import kernels
+    M, N, K = 2048, 3584, 1024
+    x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1), rnd(N, seed=2)
+    base = rnd(M, N, seed=3)
+    out = base.clone()
+    kernels.gemm_tc(x, w, out, bias, kernels.gemm.EPI_ACCUM)
+    kernels.check_tc_status()
+    want = base.double() + x.double() @ w.double().T + bias.double()
+    close(out, want, 2e-6 * math.sqrt(K), "accumulate, split last round")
+
+
 # ---- rotary encoding and cache append ----------------------------------------------
 @pytest.mark.parametrize("cache_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 5, 48, 48), (6, 2, 80, 32), (3, 1, 16, 16)])

@@ -20,6 +20,11 @@
 // Every wait on an mbarrier is bounded: when a bound is hit the role raises
 // a flag, stops, the others run into their own bounds, the block still frees
 // its TMEM, raises a bit in *status and returns: an error, not a hang.
+//
+// When the tiles do not fill the last round of the persistent blocks (224
+// tiles on 148 SMs), the residual-accumulate product cuts those last tiles
+// along K into 2 to 4 shares; the shares add into C with atomic adds, so for
+// those tiles the order of two or three float additions is not fixed.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -128,7 +133,7 @@ template <int EPI, typename TO>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const float* __restrict__ bias, TO* __restrict__ C, int M, int N, int K, int ldc, int b_rows_second,
-               int* __restrict__ status) {
+               int n_whole, int parts, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -148,7 +153,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int tiles_m = (M + TC_BM - 1) / TC_BM;
     const int tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
     const int n_tiles = tiles_m * tiles_n;
-    const int k_iters = (K + TC_BK - 1) / TC_BK;
+    const int k_all = (K + TC_BK - 1) / TC_BK;
+    // Work items: the first n_whole tiles whole; the others (a short last round, residual epilogue only) cut
+    // into `parts` shares of K each, so that the last round keeps every SM busy.  Item w -> (tile, k range).
+    const int n_items = n_whole + (n_tiles - n_whole) * parts;
+    const int k_share = (k_all + parts - 1) / parts;
+    auto item = [&](int w, int& t, int& k_lo, int& k_cnt, int& part) {
+        if (w < n_whole) { t = w; k_lo = 0; k_cnt = k_all; part = -1; return; }
+        const int r = w - n_whole;
+        t = n_whole + r / parts;
+        part = r % parts;
+        k_lo = min(k_all, part * k_share);
+        k_cnt = min(k_all, k_lo + k_share) - k_lo;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
@@ -178,7 +195,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // ---- producer: TMA loads ----
             uint32_t it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+                int t, k_lo, k_iters, part;
+                item(w, t, k_lo, k_iters, part);
                 const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * OUT_COLS;
                 for (int i = 0; i < k_iters; ++i, ++it) {
                     const int s = it % TC_STAGES;
@@ -187,12 +206,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t a_dst = smem_u32(tiles + s * TC_STAGE_BYTES);
                     const uint32_t b_dst = a_dst + TC_A_BYTES;
                     mbar_expect_tx(fb, TC_STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, i * TC_BK, m0, fb);
+                    const int kc = (k_lo + i) * TC_BK;
+                    tma_load_2d(a_dst, &map_a, kc, m0, fb);
                     if (EPI == EPI_SWIGLU) {
-                        tma_load_2d(b_dst, &map_b, i * TC_BK, n0, fb);                                  // gate rows
-                        tma_load_2d(b_dst + TC_B_BYTES / 2, &map_b, i * TC_BK, b_rows_second + n0, fb); // up rows
+                        tma_load_2d(b_dst, &map_b, kc, n0, fb);                                  // gate rows
+                        tma_load_2d(b_dst + TC_B_BYTES / 2, &map_b, kc, b_rows_second + n0, fb); // up rows
                     } else {
-                        tma_load_2d(b_dst, &map_b, i * TC_BK, n0, fb);
+                        tma_load_2d(b_dst, &map_b, kc, n0, fb);
                     }
                 }
             }
@@ -203,7 +223,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t idesc = instr_desc(TC_BM, TC_BN);
             uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local) {
+            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
+                int t, k_lo, k_iters, part;
+                item(w, t, k_lo, k_iters, part);
                 const uint32_t buf = local & 1;
                 if (!mbar_wait(smem_u32(&acc_empty[buf]), ((local >> 1) & 1) ^ 1)) { *failed = 1; ok = false; break; }
                 tc_fence_after();
@@ -231,7 +253,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         float* st = staging + (warp - 2) * 32 * 33;
         uint32_t local = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local) {
+        for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
+            int t, k_lo, k_iters, part;
+            item(w, t, k_lo, k_iters, part);
             const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * OUT_COLS;
             const uint32_t buf = local & 1;
             if (!mbar_wait(smem_u32(&acc_full[buf]), (local >> 1) & 1, true)) { *failed = 1; ok = false; break; }
@@ -257,12 +281,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int j = 0; j < 32; ++j) st[lane * 33 + j] = v[j];
                 __syncwarp();
                 const int col = n0 + c + lane;
-                const float bv = (bias && col < N) ? bias[col] : 0.f;
+                const float bv = (bias && col < N && part <= 0) ? bias[col] : 0.f;   // one share adds the bias
                 if (sizeof(TO) == 4 || EPI == EPI_ACCUM) {
                     if (col < N) {
                         const int rows = min(32, M - row0);
                         TO* out = C + (size_t)row0 * ldc + col;
-                        if (EPI == EPI_ACCUM) {
+                        if (EPI == EPI_ACCUM && part >= 0) {
+                            // a share of K: several blocks add into this tile, in whatever order they arrive
+                            for (int r = 0; r < rows; ++r)
+                                atomicAdd(reinterpret_cast<float*>(out) + (size_t)r * ldc, st[r * 33 + lane] + bv);
+                        } else if (EPI == EPI_ACCUM) {
                             // all old values first (independent loads in flight), then the sums
                             float old[32];
 #pragma unroll
@@ -341,8 +369,21 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const float* 
         if (sm_count <= 0) sm_count = 1;
     }
     const int grid = n_tiles < sm_count ? n_tiles : sm_count;
+    // The tiles of an incomplete last round are cut along K into `parts` shares (residual epilogue only: the
+    // shares add up in C), with the number of shares that lets the round end soonest: rem * parts pieces of
+    // 1 / parts of a tile each take ceil(rem * parts / grid) / parts tile times.
+    int n_whole = n_tiles, parts = 1;
+    const int rem = n_tiles % grid, k_all = (K + TC_BK - 1) / TC_BK;
+    if (EPI == EPI_ACCUM && n_tiles > grid && rem > 0) {
+        double best = 1.0;
+        for (int p = 2; p <= 8 && k_all / p >= 8; ++p) {
+            const double t = (double)((rem * p + grid - 1) / grid) / p + 0.02 * p;   // a little for each share's epilogue
+            if (t < best - 1e-9) { best = t; parts = p; }
+        }
+        if (parts > 1) n_whole = n_tiles - rem;
+    }
     gemm_tc_kernel<EPI, TO><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(ma, mb, bias, (TO*)C, M, N, K, ldc,
-                                                                        b_rows_second, status);
+                                                                        b_rows_second, n_whole, parts, status);
     return tq_launch_status();
 }
 
