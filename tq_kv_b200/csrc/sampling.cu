@@ -32,6 +32,11 @@ __device__ __forceinline__ uint32_t order_key(float x) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// the inverse of order_key
+__device__ __forceinline__ float key_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
+
 struct ArgMax { float v; int i; };
 __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
     if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
@@ -241,6 +246,186 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Fast path for 0 < top_k <= TOPK_MAX (the usual case: the reference's default
+// is 40).  Step 1: every row's vocabulary is cut into TOPK_PARTS parts; a block
+// holds its part's keys in shared memory and selects the part's top_k there
+// (every token of the row's top k is among its part's top k).  Step 2: one
+// block per row selects the row's top k among the candidates and then does
+// top-p and the draw on those few tokens with plain sorted sums.  The rules
+// are those stated at the top of this file; sums run in the same order as a
+// straightforward sorted implementation would run them.
+// ---------------------------------------------------------------------------
+#define TOPK_MAX 64
+#define TOPK_PARTS 32
+#define TOPK_CAP 128            // candidates kept per part (top_k plus ties at the cut)
+#define TOPK_PART_MAX 8192      // largest part held in shared memory: vocabularies up to 262,144
+#define TOPK_KEEP_MAX 512       // tokens kept per row after top-k (top_k plus ties at the cut)
+
+// key of the k-th largest among n keys in shared memory (k <= n); all threads of the block call it
+__device__ uint32_t block_kth_largest(const uint32_t* keys, int n, int k, int* hist, uint32_t* sh_prefix,
+                                      int* sh_remaining) {
+    uint32_t prefix = 0, mask = 0;
+    int remaining = k;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const uint32_t key = keys[i];
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int cum = 0, sel = 0;
+            for (int b = 255; b >= 0; --b) {
+                if (cum + hist[b] >= remaining) { sel = b; break; }
+                cum += hist[b];
+            }
+            *sh_prefix = prefix | ((uint32_t)sel << shift);
+            *sh_remaining = remaining - cum;
+        }
+        __syncthreads();
+        prefix = *sh_prefix;
+        remaining = *sh_remaining;
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    return prefix;
+}
+
+__global__ void __launch_bounds__(256)
+topk_parts_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ counts, float penalty,
+                  int top_k, float* __restrict__ cand_val, int* __restrict__ cand_idx, int* __restrict__ cand_cnt) {
+    __shared__ uint32_t keys[TOPK_PART_MAX];
+    __shared__ int hist[256];
+    __shared__ uint32_t sh_prefix;
+    __shared__ int sh_remaining, sh_count;
+    const int row = blockIdx.x, part = blockIdx.y;
+    pdl_wait();
+    pdl_launch();
+    const float* lg = logits + (size_t)row * ld;
+    const int* cnt = counts ? counts + (size_t)row * V : nullptr;
+    const int per = (V + TOPK_PARTS - 1) / TOPK_PARTS;
+    const int lo = part * per, n = max(0, min(V, lo + per) - lo);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) keys[i] = order_key(penalised(lg, cnt, penalty, lo + i));
+    if (threadIdx.x == 0) sh_count = 0;
+    __syncthreads();
+    uint32_t kth = 0;
+    if (n > top_k) kth = block_kth_largest(keys, n, top_k, hist, &sh_prefix, &sh_remaining);
+    const size_t base = ((size_t)row * TOPK_PARTS + part) * TOPK_CAP;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        if (keys[i] >= kth) {
+            const int slot = atomicAdd(&sh_count, 1);
+            if (slot < TOPK_CAP) {
+                cand_val[base + slot] = penalised(lg, cnt, penalty, lo + i);
+                cand_idx[base + slot] = lo + i;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) cand_cnt[row * TOPK_PARTS + part] = min(sh_count, TOPK_CAP);
+}
+
+__global__ void __launch_bounds__(256)
+topk_final_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_idx,
+                  const int* __restrict__ cand_cnt, int V, float temperature, int top_k, float top_p,
+                  const float* __restrict__ uniforms, int* __restrict__ counts, int* __restrict__ out) {
+    __shared__ uint32_t keys[TOPK_PARTS * TOPK_CAP];             // order keys of the candidates' logits
+    __shared__ int idxs[TOPK_PARTS * TOPK_CAP];
+    __shared__ float kp[TOPK_KEEP_MAX], sp[TOPK_KEEP_MAX];       // kept probabilities; the same, sorted
+    __shared__ int ki[TOPK_KEEP_MAX], si[TOPK_KEEP_MAX];         // kept token ids; ids in sorted order
+    __shared__ int hist[256];
+    __shared__ uint32_t sh_prefix;
+    __shared__ int sh_remaining, sh_n, sh_kept;
+    __shared__ float sh_cut;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    pdl_wait();
+    pdl_launch();
+    // gather the candidates of all parts
+    if (tid == 0) { sh_n = 0; sh_kept = 0; }
+    __syncthreads();
+    for (int part = 0; part < TOPK_PARTS; ++part) {
+        const int c = cand_cnt[row * TOPK_PARTS + part];
+        const size_t base = ((size_t)row * TOPK_PARTS + part) * TOPK_CAP;
+        __shared__ int sh_off;
+        if (tid == 0) { sh_off = sh_n; sh_n += c; }
+        __syncthreads();
+        for (int i = tid; i < c; i += blockDim.x) {
+            idxs[sh_off + i] = cand_idx[base + i];
+            keys[sh_off + i] = order_key(cand_val[base + i]);
+        }
+        __syncthreads();
+    }
+    const int n = sh_n;
+    uint32_t kth = 0;
+    if (n > top_k) kth = block_kth_largest(keys, n, top_k, hist, &sh_prefix, &sh_remaining);
+    // the row's maximum and the kept tokens (logit >= the k-th largest)
+    float mx = -INFINITY;
+    for (int i = tid; i < n; i += blockDim.x) mx = fmaxf(mx, key_value(keys[i]));
+    __shared__ float red[32];
+    mx = block_max(mx, red);
+    for (int i = tid; i < n; i += blockDim.x) {
+        if (keys[i] >= kth) {
+            const int slot = atomicAdd(&sh_kept, 1);
+            if (slot < TOPK_KEEP_MAX) {
+                kp[slot] = expf((key_value(keys[i]) - mx) / temperature);
+                ki[slot] = idxs[i];
+            }
+        }
+    }
+    __syncthreads();
+    const int m = min(sh_kept, TOPK_KEEP_MAX);
+    // top-p: sort by probability (descending, lower id first on ties), running mass in float64
+    for (int e = tid; e < m; e += blockDim.x) {
+        int rank = 0;
+        for (int j = 0; j < m; ++j) rank += (kp[j] > kp[e] || (kp[j] == kp[e] && ki[j] < ki[e])) ? 1 : 0;
+        sp[rank] = kp[e];
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float cut = 0.f;
+        if (top_p < 1.f) {
+            double total = 0.0;
+            for (int j = 0; j < m; ++j) total += (double)sp[j];
+            const double target = (double)top_p * total;
+            double cum = 0.0;
+            cut = sp[m - 1];
+            for (int j = 0; j < m; ++j) {
+                cum += (double)sp[j];
+                if (cum >= target) { cut = sp[j]; break; }
+            }
+        }
+        sh_cut = cut;
+    }
+    __syncthreads();
+    const float cut = sh_cut;
+    // the draw: kept tokens in token-id order
+    for (int e = tid; e < m; e += blockDim.x) {
+        int rank = 0;
+        for (int j = 0; j < m; ++j) rank += (ki[j] < ki[e]) ? 1 : 0;
+        si[rank] = ki[e];
+        sp[rank] = kp[e] >= cut ? kp[e] : 0.f;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        double total = 0.0;
+        for (int j = 0; j < m; ++j) total += (double)sp[j];
+        const double target = (double)uniforms[row] * total;
+        double cum = 0.0;
+        int tok = -1, last = -1;
+        for (int j = 0; j < m; ++j) {
+            if (sp[j] > 0.f) last = si[j];
+            cum += (double)sp[j];
+            if (cum > target) { tok = si[j]; break; }
+        }
+        if (tok < 0) tok = last;
+        out[row] = tok;
+        if (counts) counts[(size_t)row * V + tok] += 1;
+    }
+}
+
 // Arg-max in two steps for speed: the vocabulary of a row is cut into ARGMAX_PARTS parts, one block each;
 // a second kernel picks the best part (lowest id on ties) and counts the chosen token.
 #define ARGMAX_PARTS 32
@@ -282,7 +467,12 @@ __global__ void argmax_final_kernel(const ArgMax* __restrict__ parts, int* __res
 // counts: int32 [rows, V] occurrence counts of generated tokens (or null);
 // the sampled token's count is incremented.  uniforms: float [rows] in [0, 1)
 // (unused when temperature <= 0).
-// scratch: optional, 8 * 32 bytes per row; with it, arg-max runs as two short kernels on many blocks.
+// scratch: optional, tq_sample_scratch_bytes(rows) bytes; with it, arg-max and sampling with
+// 0 < top_k <= 64 run as two short kernels on many blocks instead of one block per row.
+TQ_API size_t tq_sample_scratch_bytes(int n_rows) {
+    return (size_t)n_rows * TOPK_PARTS * (TOPK_CAP * 8 + 4) + 256;
+}
+
 TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float temperature, int top_k, float top_p,
                      const float* uniforms, int* counts, float penalty, int* out, void* scratch,
                      cudaStream_t stream) {
@@ -296,6 +486,18 @@ TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float tempe
         if (st) return st;
         return tq_launch_pdl(argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, (const ArgMax*)scratch, counts, V,
                              out);
+    }
+    if (temperature > 0.f && scratch && top_k > 0 && top_k <= TOPK_MAX && n_rows <= 65535 &&
+        (V + TOPK_PARTS - 1) / TOPK_PARTS <= TOPK_PART_MAX) {
+        float* cand_val = (float*)scratch;
+        int* cand_idx = (int*)(cand_val + (size_t)n_rows * TOPK_PARTS * TOPK_CAP);
+        int* cand_cnt = cand_idx + (size_t)n_rows * TOPK_PARTS * TOPK_CAP;
+        int st = tq_launch_pdl(topk_parts_kernel, dim3(n_rows, TOPK_PARTS), dim3(256), 0, stream, logits, ld, V,
+                               (const int*)counts, penalty, top_k, cand_val, cand_idx, cand_cnt);
+        if (st) return st;
+        return tq_launch_pdl(topk_final_kernel, dim3(n_rows), dim3(256), 0, stream, (const float*)cand_val,
+                             (const int*)cand_idx, (const int*)cand_cnt, V, temperature, top_k, top_p, uniforms,
+                             counts, out);
     }
     return tq_launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
                          top_k, top_p, uniforms, counts, penalty, out);

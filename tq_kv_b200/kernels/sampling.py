@@ -1,6 +1,7 @@
 """Python entry point of the sampling kernel (csrc/sampling.cu)."""
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -28,20 +29,25 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float = 0.0,
         raise KernelError("sample: counts must be int32 [R, V]")
     need_contiguous(out=out, uniforms=uniforms, counts=counts)
     scratch = None
-    if temperature <= 0:
-        scratch = _argmax_scratch(logits.device, R)
+    if temperature <= 0 or 0 < top_k <= FAST_TOP_K_MAX:
+        scratch = _sample_scratch(logits.device, R)
     check(core().tq_sample(ptr(logits), logits.stride(0), R, V, float(temperature), int(top_k), float(top_p),
                            ptr(uniforms), ptr(counts), float(repeat_penalty), ptr(out), ptr(scratch), stream()),
           "sample", 2 if scratch is not None else 1)
     return out
 
 
+FAST_TOP_K_MAX = 64
 _scratch: dict = {}
 
 
-def _argmax_scratch(device, rows: int) -> torch.Tensor:
-    """(value, index) pairs of the arg-max's first step: 32 per row, kept per device and grown on demand."""
+def _sample_scratch(device, rows: int) -> torch.Tensor:
+    """Candidates of the two-step kernels (arg-max parts, top-k parts): kept per device, grown on demand."""
+    lib = core()
+    lib.tq_sample_scratch_bytes.restype = ctypes.c_size_t
+    lib.tq_sample_scratch_bytes.argtypes = [ctypes.c_int]
+    need = int(lib.tq_sample_scratch_bytes(max(rows, 64)))
     t = _scratch.get(device)
-    if t is None or t.numel() < rows * 64:
-        t = _scratch[device] = torch.empty(max(rows, 64) * 64, dtype=torch.int32, device=device)
+    if t is None or t.numel() < need:
+        t = _scratch[device] = torch.empty(need, dtype=torch.uint8, device=device)
     return t
