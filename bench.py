@@ -240,7 +240,7 @@ def main() -> int:
         d2h = stats.get("d2h_bytes", 0) / steps_total
 
     rec = {
-        "metric": "decode tok/s (Qwen2.5-7B shape, bf16 random weights)", "value": round(value, 1),
+        "metric": f"decode tok/s ({args.shape} shape, bf16 random weights)", "value": round(value, 1),
         "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours", "gpu_launches": launches,

@@ -218,6 +218,23 @@ def test_gemm_tc_accumulate_with_a_short_last_round():
     close(out, want, 2e-6 * math.sqrt(K), "accumulate, split last round")
 
 
+def test_a_wait_that_ran_out_is_reported_by_the_host_check():
+    """The tcgen05 kernels bound every mbarrier wait and raise a status bit instead of hanging.  No wait is made
+    to run out here (that would need a kernel that misbehaves on purpose); the status word is set by hand and the
+    host-side check must turn it into an error and clear it."""
+    from tq_kv_b200 import kernels
+    x, w = rnd(128, 64, dtype=torch.bfloat16), rnd(256, 64, dtype=torch.bfloat16, seed=1)
+    out = torch.empty(128, 256, device=DEV)
+    kernels.gemm_tc(x, w, out)
+    kernels.check_tc_status()                                        # a healthy launch passes
+    kernels.gemm_tc(x, w, out)
+    kernels.gemm._status_for(x.device).fill_(2)
+    with pytest.raises(kernels.KernelError, match="wait ran out"):
+        kernels.check_tc_status()
+    kernels.gemm_tc(x, w, out)
+    kernels.check_tc_status()                                        # the word was cleared
+
+
 # ---- rotary encoding and cache append ----------------------------------------------
 @pytest.mark.parametrize("cache_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 5, 48, 48), (6, 2, 80, 32), (3, 1, 16, 16)])

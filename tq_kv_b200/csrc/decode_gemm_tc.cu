@@ -196,24 +196,37 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
         for (int p = 0; p < 8; ++p) peers[p] = p < n_ranks ? cluster.map_shared_rank(red, p) : red;
         const int runs = (OUT_COLS / 32) * M;
-        for (int q = rank + n_ranks * (threadIdx.x >> 5); q < runs; q += n_ranks * (DG_THREADS / 32)) {
-            const int m = q / (OUT_COLS / 32), c = (q - m * (OUT_COLS / 32)) * 32 + lane;
-            const int col = n0 + c;
-            float pv[8], pu[8];
+        const int step = n_ranks * (DG_THREADS / 32);
+        // four runs per turn: all their (remote) reads are in flight before the first sum
+        for (int q0 = rank + n_ranks * (threadIdx.x >> 5); q0 < runs; q0 += 4 * step) {
+            float pv[4][8], pu[4][8];
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {                     // all remote reads are issued before the first add
-                pv[p] = p < n_ranks ? peers[p][c * RED_LD + m] : 0.f;
-                pu[p] = (SWIGLU && p < n_ranks) ? peers[p][(c + OUT_COLS) * RED_LD + m] : 0.f;
+            for (int u = 0; u < 4; ++u) {
+                const int q = q0 + u * step;
+                const int m = q / (OUT_COLS / 32), c = (q - m * (OUT_COLS / 32)) * 32 + lane;
+#pragma unroll
+                for (int p = 0; p < 8; ++p) {
+                    const bool on = q < runs && p < n_ranks;
+                    pv[u][p] = on ? peers[p][c * RED_LD + m] : 0.f;
+                    pu[u][p] = (SWIGLU && on) ? peers[p][(c + OUT_COLS) * RED_LD + m] : 0.f;
+                }
             }
-            float v = pv[0], u = pu[0];
 #pragma unroll
-            for (int p = 1; p < 8; ++p) { v += pv[p]; u += pu[p]; }
-            if (col >= N) continue;
-            if (bias) { v += bias[col]; if (SWIGLU) u += bias[col + N]; }
-            if (SWIGLU) v = (v / (1.f + expf(-v))) * u;
-            TO* y = Y + (size_t)m * ldy + col;
-            if (accumulate) v += to_f32<TO>(*y);
-            *y = from_f32<TO>(v);
+            for (int u = 0; u < 4; ++u) {
+                const int q = q0 + u * step;
+                if (q >= runs) continue;
+                const int m = q / (OUT_COLS / 32), c = (q - m * (OUT_COLS / 32)) * 32 + lane;
+                const int col = n0 + c;
+                float v = pv[u][0], w = pu[u][0];
+#pragma unroll
+                for (int p = 1; p < 8; ++p) { v += pv[u][p]; w += pu[u][p]; }
+                if (col >= N) continue;
+                if (bias) { v += bias[col]; if (SWIGLU) w += bias[col + N]; }
+                if (SWIGLU) v = (v / (1.f + expf(-v))) * w;
+                TO* y = Y + (size_t)m * ldy + col;
+                if (accumulate) v += to_f32<TO>(*y);
+                *y = from_f32<TO>(v);
+            }
         }
     }
     if (n_ranks > 1) cluster.sync(); else __syncthreads();   // peers keep their shared memory until it was read

@@ -2,7 +2,7 @@
 // for memory bandwidth: one block per (token, key/value head, split of the
 // key range); the q heads that share the key/value head form the rows of one
 // 16-row tensor-core tile, so every key and value is read once for all of
-// them.  Each of the 4 warps owns every fourth 16-key chunk of the split and
+// them.  Each of the 4 warps owns every fourth 16- or 32-key chunk of the split and
 // streams it global -> shared with cp.async (3 stages per warp, no block
 // barrier in the loop), computes S = Q·K^T and O += P·V with mma.sync
 // m16n8k16, keeps a float32 online softmax per row, and the warps' states
@@ -14,7 +14,6 @@
 
 #define FD_WARPS 4
 #define FD_STAGES 3
-#define FD_CHUNK 16          // keys per warp iteration
 #define FD_PAGE 64           // tokens per cache page (checked by the launcher)
 
 __device__ __forceinline__ void fd_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
@@ -44,7 +43,8 @@ __device__ __forceinline__ uint32_t fd_pack(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD>
+// FD_CHUNK: keys per warp iteration — 16, or 32 for heads of up to 64 dims, whose 16-key chunks would be too small.
+template <int HD, int FD_CHUNK>
 __global__ void __launch_bounds__(FD_WARPS * 32)
 flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                     const int* __restrict__ block_table, int table_width, int ring_pages,
@@ -91,14 +91,14 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         }
     }
 
-    // issue the copy of this warp's i-th chunk into stage i % FD_STAGES.  Lane l < 16 looks up the row of
-    // key l; then consecutive lanes copy consecutive 16-byte pieces of a row, so that every 32-byte sector
-    // is asked for once.
+    // issue the copy of this warp's i-th chunk into stage i % FD_STAGES.  Lane l < FD_CHUNK looks up the row
+    // of key l; then consecutive lanes copy consecutive 16-byte pieces of a row, so that every 32-byte
+    // sector is asked for once.
     constexpr int PR = HD / 8;                              // 16-byte pieces per row
     auto issue = [&](int i) {
         const int chunk = warp + i * FD_WARPS;
         if (chunk < n_chunks) {
-            int j = lo + chunk * FD_CHUNK + (lane & 15);
+            int j = lo + chunk * FD_CHUNK + (lane & (FD_CHUNK - 1));
             if (j >= hi) j = hi - 1;                       // a valid address; the score is masked
             int lp = j / FD_PAGE;
             if (ring_pages > 0) lp %= ring_pages;
@@ -106,7 +106,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
             unsigned char* ks_ = my + (i % FD_STAGES) * 2 * TILE;
             unsigned char* vs_ = ks_ + TILE;
 #pragma unroll
-            for (int it = 0; it < PR / 2; ++it) {
+            for (int it = 0; it < FD_CHUNK * PR / 32; ++it) {
                 const int p = lane + 32 * it;
                 const int key = p / PR, c = p - key * PR;
                 const unsigned long long row = __shfl_sync(0xffffffffu, my_row, key);
@@ -133,20 +133,26 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         const unsigned char* vs_ = ks_ + TILE;
         const int j0 = lo + (warp + i * FD_WARPS) * FD_CHUNK;
 
-        // S[16 heads x 16 keys] = Q · K^T
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // S[16 heads x FD_CHUNK keys] = Q · K^T
+        constexpr int ST = FD_CHUNK / 8;                   // 8-key tiles of S
+        float s[ST][4];
+#pragma unroll
+        for (int n = 0; n < ST; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            uint32_t kb[4];
-            const int mat = lane >> 3, r = lane & 7;
-            fd_ldmatrix_x4(kb, ks_ + ((mat >> 1) * 8 + r) * ROW + (2 * ks + (mat & 1)) * 16);
-            fd_mma(s[0], qf[ks], kb[0], kb[1]);
-            fd_mma(s[1], qf[ks], kb[2], kb[3]);
+#pragma unroll
+            for (int n = 0; n < ST; n += 2) {
+                uint32_t kb[4];
+                const int mat = lane >> 3, r = lane & 7;
+                fd_ldmatrix_x4(kb, ks_ + ((n + (mat >> 1)) * 8 + r) * ROW + (2 * ks + (mat & 1)) * 16);
+                fd_mma(s[n], qf[ks], kb[0], kb[1]);
+                fd_mma(s[n + 1], qf[ks], kb[2], kb[3]);
+            }
         }
         // scale, mask keys beyond the range, online softmax (rows gid and gid + 8)
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < ST; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int j = j0 + nt * 8 + 2 * tid4 + (e & 1);
@@ -165,7 +171,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         }
         float rs[2] = {0.f, 0.f};
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < ST; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float p = exp2f(s[nt][e] - m_run[e >> 1]);
@@ -178,19 +184,24 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
             rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
             l_run[r] = l_run[r] * corr[r] + rs[r];
         }
-        uint32_t pf[4] = {fd_pack(s[0][0], s[0][1]), fd_pack(s[0][2], s[0][3]), fd_pack(s[1][0], s[1][1]),
-                          fd_pack(s[1][2], s[1][3])};
-        // O = O * corr + P · V
+        // O = O * corr + P · V, 16 keys per k-step
 #pragma unroll
-        for (int n = 0; n < NT; n += 2) {
-            uint32_t vb[4];
-            const int mat = lane >> 3, r = lane & 7;
-            fd_ldmatrix_x4_trans(vb, vs_ + ((mat & 1) * 8 + r) * ROW + (n + (mat >> 1)) * 16);
+        for (int n = 0; n < NT; ++n) {
+            o[n][0] *= corr[0]; o[n][1] *= corr[0];
+            o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                o[n + h][0] *= corr[0]; o[n + h][1] *= corr[0];
-                o[n + h][2] *= corr[1]; o[n + h][3] *= corr[1];
-                fd_mma(o[n + h], pf, vb[2 * h], vb[2 * h + 1]);
+        for (int kk = 0; kk < FD_CHUNK / 16; ++kk) {
+            const uint32_t pf[4] = {fd_pack(s[2 * kk][0], s[2 * kk][1]), fd_pack(s[2 * kk][2], s[2 * kk][3]),
+                                    fd_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]),
+                                    fd_pack(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+            for (int n = 0; n < NT; n += 2) {
+                uint32_t vb[4];
+                const int mat = lane >> 3, r = lane & 7;
+                fd_ldmatrix_x4_trans(vb, vs_ + (kk * 16 + (mat & 1) * 8 + r) * ROW + (n + (mat >> 1)) * 16);
+                fd_mma(o[n], pf, vb[0], vb[1]);
+                fd_mma(o[n + 1], pf, vb[2], vb[3]);
             }
         }
         __syncwarp();                                      // the stage may be overwritten by the next issue
@@ -254,18 +265,19 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
                                bf16* out, float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int n_splits,
                                cudaStream_t stream) {
     constexpr int ROW = HD * 2 + 16;
+    constexpr int FD_CHUNK = HD <= 64 ? 32 : 16;
     constexpr size_t stage_bytes = (size_t)FD_WARPS * FD_STAGES * 2 * FD_CHUNK * ROW;
     constexpr size_t merge_bytes = (size_t)FD_WARPS * 16 * (HD + 2) * sizeof(float);
     constexpr size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<HD, FD_CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const dim3 grid(n_tokens, nkv, n_splits);
-    return tq_launch_pdl(flash_decode_kernel<HD>, grid, dim3(FD_WARPS * 32), smem, stream, q, kp, vp, table,
+    return tq_launch_pdl(flash_decode_kernel<HD, FD_CHUNK>, grid, dim3(FD_WARPS * 32), smem, stream, q, kp, vp, table,
                          table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out, part_acc,
                          part_ml, nh, nkv, n_splits);
 }
