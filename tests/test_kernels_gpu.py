@@ -328,10 +328,15 @@ def plain_attention(q, k, v, nh, nkv, hd, window, q_pos):
 @pytest.mark.parametrize("nh,nkv,hd,window", [(7, 1, 128, None), (6, 3, 48, 20), (5, 5, 16, None), (16, 2, 256, 33),
                                               (24, 2, 80, None), (4, 2, 64, 70), (3, 3, 96, None), (2, 1, 32, 5),
                                               (14, 2, 128, 129)])
-@pytest.mark.parametrize("lens", [[1, 37, 90], [200, 64, 3, 129]])
-@pytest.mark.parametrize("flash", [True, False])
-def test_attention_over_packed_prompts(dtype, nh, nkv, hd, window, lens, flash):
+@pytest.mark.parametrize("lens", [[1, 37, 90], [200, 64, 3, 129], [300]])
+@pytest.mark.parametrize("flash", ["tcgen05", "mma", "general"])
+def test_attention_over_packed_prompts(dtype, nh, nkv, hd, window, lens, flash, monkeypatch):
+    """Three kernels for prompts: tcgen05 (heads of 64 and 128), mma.sync (32..128), the general one."""
     from tq_kv_b200 import kernels
+    import importlib
+    att = importlib.import_module("tq_kv_b200.kernels.attention")   # (the package exports a function of that name)
+    monkeypatch.setattr(att, "USE_TC_ATTENTION", flash == "tcgen05")
+    flash = flash != "general"
     T = sum(lens)
     q, k, v = rnd(T, nh * hd, dtype=dtype), rnd(T, nkv * hd, dtype=dtype, seed=1), rnd(T, nkv * hd, dtype=dtype, seed=2)
     cu = [0]
@@ -443,8 +448,12 @@ def test_prompt_chunks_attend_over_the_paged_cache():
     T = sum(lens)
     q = rnd(T, nh * hd, dtype=dtype)
     pos = sum((list(range(s, s + n)) for s, n in zip(starts, lens)), [])
+    import importlib
+    att = importlib.import_module("tq_kv_b200.kernels.attention")
     for window in (None, 100):
-        for flash in (True, False):
+        for flash in ("tcgen05", "mma", "general"):
+            att.USE_TC_ATTENTION = flash == "tcgen05"
+            flash = flash != "general"
             out = torch.empty_like(q)
             kernels.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
                               tok_pos=torch.tensor(pos, dtype=torch.int32, device=DEV),
@@ -459,6 +468,8 @@ def test_prompt_chunks_attend_over_the_paged_cache():
                                        list(range(starts[b], starts[b] + lens[b])))
                 close(out[a:a + lens[b]], want, 8e-3, f"row {b}, window {window}, flash {flash}")
                 a += lens[b]
+    att.USE_TC_ATTENTION = True
+    kernels.check_tc_status()
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 8e-3)])

@@ -1,0 +1,379 @@
+// Causal grouped-query attention for prompts on the tcgen05 tensor cores.
+//
+// A block owns 128 consecutive query tokens of one (sequence, q head) and walks
+// the keys in tiles of 128.  Per tile:
+//   S  = Q · K^T      tcgen05.mma, Q and K tiles K-major in shared memory (TMA,
+//                     128-byte swizzle), S[128 x 128] float32 in TMEM;
+//   softmax           four warps, one query row per thread (TMEM lane = row, so
+//                     the row maximum and sum need no shuffles), float32, with a
+//                     running maximum; P is written to shared memory as bfloat16
+//                     in the swizzled K-major layout the next MMA reads;
+//   PV = P · V        tcgen05.mma with V as an MN-major operand (the V tile is
+//                     [keys][head_dim] as it lies in memory), result in TMEM;
+//   O  = O * c + PV   in registers (one row of head_dim floats per thread).
+// Roles: warp 0 lane 0 issues TMA loads (Q once, K/V tiles through two stages),
+// warp 1 lane 0 issues the MMAs, warps 2..5 do softmax, accumulation and the
+// final store.  Keys and values come from the step's packed rows (PAGED =
+// false) or from the paged cache (two 64-token pages per tile).  An optional
+// sliding window narrows the key range; tiles outside a block's range are
+// never loaded.  All mbarrier waits are bounded (see gemm_tc.cu).
+//
+// Formulas: src/models/turbo_generic.rs:1620-1631 (see attention.cu).
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define FT_BM 128
+#define FT_BN 128
+#define FT_THREADS 192
+#define FT_SUB_BYTES (128 * 128)          // a [128 rows x 64 bf16] sub-tile
+#define FT_WAIT_CYCLES (4000000000ll)
+
+__device__ __forceinline__ uint32_t ft_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool ft_wait(uint32_t bar, uint32_t parity, bool backoff = false) {
+    const long long t0 = clock64();
+    for (uint32_t i = 1;; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if (backoff) __nanosleep(100);
+        if ((i & 255u) == 0 && clock64() - t0 > FT_WAIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void ft_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void ft_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ft_tma(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ft_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void ft_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void ft_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t ft_desc_k(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand, 128-byte swizzle: a row holds 64 MN elements of one k; 8 k-rows form a 1024-byte group
+// (stride byte offset); the next 64 MN elements lie `mn_stride` bytes further (leading byte offset)
+__device__ __forceinline__ uint64_t ft_desc_mn(uint32_t saddr, uint32_t mn_stride) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((mn_stride >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+template <int HD, bool PAGED>
+__global__ void __launch_bounds__(FT_THREADS, 1)
+flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
+                        int ring_pages, const int* __restrict__ cu_seqlens, const int* __restrict__ start_pos,
+                        int n_seqs, int window, float scale_log2, bf16* __restrict__ out, int nh, int nkv,
+                        int* __restrict__ status) {
+    constexpr int SUBS = HD / 64;                          // 64-column sub-tiles of a Q, K or V tile
+    constexpr int TILE_BYTES = SUBS * FT_SUB_BYTES;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = base;
+    unsigned char* k_s = q_s + TILE_BYTES;                 // [2 stages]
+    unsigned char* v_s = k_s + 2 * TILE_BYTES;             // [2 stages]
+    unsigned char* p_s = v_s + 2 * TILE_BYTES;             // P: two sub-tiles of 64 keys
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * FT_SUB_BYTES);
+    uint64_t* q_full = bars;                               // 1
+    uint64_t* kv_full = bars + 1;                          // [2]
+    uint64_t* kv_empty = bars + 3;                         // [2]
+    uint64_t* s_full = bars + 5;
+    uint64_t* p_full = bars + 6;                           // 128 arrivals (softmax threads)
+    uint64_t* o_full = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile uint32_t* failed = tmem_slot + 1;
+
+    // which (sequence, 128-token tile) is this block's?
+    int b = -1, tile = blockIdx.x;
+    for (int i = 0; i < n_seqs; ++i) {
+        const int tiles = (cu_seqlens[i + 1] - cu_seqlens[i] + FT_BM - 1) / FT_BM;
+        if (tile < tiles) { b = i; break; }
+        tile -= tiles;
+    }
+    if (b < 0) return;
+    const int h = blockIdx.y, g = h / (nh / nkv);
+    const int tok0 = cu_seqlens[b], len = cu_seqlens[b + 1] - tok0, start = start_pos[b];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p_first = start + tile * FT_BM;
+    const int p_last = start + min(len, tile * FT_BM + FT_BM) - 1;
+    int j_begin = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+    j_begin &= ~(FT_BN - 1);
+    const int n_tiles = (p_last - j_begin) / FT_BN + 1;
+
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(q_full)));
+        for (int s = 0; s < 2; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&kv_full[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&kv_empty[s])));
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(s_full)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;\n" ::"r"(ft_smem(p_full)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(o_full)));
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(ft_smem(tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_s = *tmem_slot;                    // S: columns 0..127
+    const uint32_t tmem_o = tmem_s + 128;                  // P·V of the current tile: columns 128..128+HD
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer ----
+            ft_expect(ft_smem(q_full), TILE_BYTES);
+            for (int sub = 0; sub < SUBS; ++sub)
+                ft_tma(ft_smem(q_s + sub * FT_SUB_BYTES), &map_q, h * HD + sub * 64, tok0 + tile * FT_BM, ft_smem(q_full));
+            for (int it = 0; it < n_tiles; ++it) {
+                const int s = it & 1;
+                if (!ft_wait(ft_smem(&kv_empty[s]), ((it >> 1) & 1) ^ 1)) { *failed = 1; break; }
+                const uint32_t fb = ft_smem(&kv_full[s]);
+                ft_expect(fb, 2 * TILE_BYTES);
+                const int j0 = j_begin + it * FT_BN;
+                if (PAGED) {
+                    for (int half = 0; half < 2; ++half) {
+                        int lp = (j0 + 64 * half) / 64;
+                        if (ring_pages > 0) lp %= ring_pages;
+                        // pages past the sequence's last one are not in the table: any valid page will do (masked)
+                        const int last_lp = ring_pages > 0 ? (p_last / 64) % ring_pages : p_last / 64;
+                        if (j0 + 64 * half > p_last) lp = last_lp;
+                        const int row = (block_table[(size_t)b * table_width + lp] * nkv + g) * 64;
+                        for (int sub = 0; sub < SUBS; ++sub) {
+                            ft_tma(ft_smem(k_s + s * TILE_BYTES + sub * FT_SUB_BYTES + half * 8192), &map_k, sub * 64, row, fb);
+                            ft_tma(ft_smem(v_s + s * TILE_BYTES + sub * FT_SUB_BYTES + half * 8192), &map_v, sub * 64, row, fb);
+                        }
+                    }
+                } else {
+                    const int row = tok0 - start + j0;       // key j lives at packed token tok0 - start + j
+                    for (int sub = 0; sub < SUBS; ++sub) {
+                        ft_tma(ft_smem(k_s + s * TILE_BYTES + sub * FT_SUB_BYTES), &map_k, g * HD + sub * 64, row, fb);
+                        ft_tma(ft_smem(v_s + s * TILE_BYTES + sub * FT_SUB_BYTES), &map_v, g * HD + sub * 64, row, fb);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_BN >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
+            const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* B is MN-major */ |
+                                     ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
+            bool ok = ft_wait(ft_smem(q_full), 0);
+            if (!ok) *failed = 1;
+            for (int it = 0; it < n_tiles && ok; ++it) {
+                const int s = it & 1;
+                if (!ft_wait(ft_smem(&kv_full[s]), (it >> 1) & 1)) { *failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t qa = ft_smem(q_s), ka = ft_smem(k_s + s * TILE_BYTES), va = ft_smem(v_s + s * TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {       // S = Q · K^T over head_dim
+                    const uint32_t off = (ks >> 2) * FT_SUB_BYTES + (ks & 3) * 32;
+                    ft_mma(tmem_s, ft_desc_k(qa + off), ft_desc_k(ka + off), idesc_s, ks > 0 ? 1u : 0u);
+                }
+                ft_commit(ft_smem(s_full));
+                if (!ft_wait(ft_smem(p_full), it & 1)) { *failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t pa = ft_smem(p_s);
+#pragma unroll
+                for (int ks = 0; ks < FT_BN / 16; ++ks) {    // P·V over the tile's 128 keys
+                    const uint32_t a_off = (ks >> 2) * FT_SUB_BYTES + (ks & 3) * 32;
+                    ft_mma(tmem_o, ft_desc_k(pa + a_off), ft_desc_mn(va + ks * 2048, FT_SUB_BYTES), idesc_o, ks > 0 ? 1u : 0u);
+                }
+                ft_commit(ft_smem(&kv_empty[s]));            // the stage is free once these MMAs are done
+                ft_commit(ft_smem(o_full));
+            }
+        }
+    } else {
+        // ---- softmax, accumulation, store: thread = query row ----
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                   // row of the tile = TMEM lane
+        const int i_row = tile * FT_BM + r;                  // token index within the sequence
+        const int p_row = start + min(i_row, len - 1);       // rows past the end repeat the last row (never stored)
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        float m_run = -INFINITY, l_run = 0.f;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        bool ok = true;
+        for (int it = 0; it < n_tiles && ok; ++it) {
+            const int j0 = j_begin + it * FT_BN;
+            if (!ft_wait(ft_smem(s_full), it & 1, true)) { *failed = 1; ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            // key j is seen iff p_row - window < j <= p_row
+            const int j_hi = p_row, j_lo = window > 0 ? p_row - window + 1 : 0;
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < FT_BN; c += 32) {
+                float v[32];
+                ft_ld32(tmem_s + lane_addr + c, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int key = j0 + c + j;
+                    if (key >= j_lo && key <= j_hi) mx = fmaxf(mx, v[j]);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx * scale_log2);
+            const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+            m_run = m_new;
+            float rs = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < FT_BN; c += 32) {
+                float v[32];
+                ft_ld32(tmem_s + lane_addr + c, v);
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const int key = j0 + c + j;
+                    float p0 = (key >= j_lo && key <= j_hi && m_new > -INFINITY) ? exp2f(v[j] * scale_log2 - m_new) : 0.f;
+                    float p1 = (key + 1 >= j_lo && key + 1 <= j_hi && m_new > -INFINITY) ? exp2f(v[j + 1] * scale_log2 - m_new) : 0.f;
+                    rs += p0 + p1;
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                    packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+                }
+                // 32 keys = four 16-byte chunks of this row, in the swizzled K-major layout
+                unsigned char* prow = p_s + (c >> 6) * FT_SUB_BYTES + r * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = ((c & 63) >> 3) + q4;
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
+                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+            }
+            l_run = l_run * corr + rs;
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P is read by the tensor core
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            ft_arrive(ft_smem(p_full));
+            if (!ft_wait(ft_smem(o_full), it & 1, true)) { *failed = 1; ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < HD; c += 32) {
+                float v[32];
+                ft_ld32(tmem_o + lane_addr + c, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * corr + v[j];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        }
+        if (ok && i_row < len) {
+            const float inv = 1.f / l_run;
+            bf16* orow = out + ((size_t)(tok0 + i_row) * nh + h) * HD;
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(o[d] * inv, o[d + 1] * inv);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(o[d + 2] * inv, o[d + 3] * inv);
+                __nv_bfloat162 c2 = __floats2bfloat162_rn(o[d + 4] * inv, o[d + 5] * inv);
+                __nv_bfloat162 d2 = __floats2bfloat162_rn(o[d + 6] * inv, o[d + 7] * inv);
+                *reinterpret_cast<uint4*>(orow + d) = make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b2),
+                                                                 *reinterpret_cast<uint32_t*>(&c2), *reinterpret_cast<uint32_t*>(&d2));
+            }
+        }
+    }
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0 && *failed && status) atomicOr(status, 4);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(256u) : "memory");
+    }
+}
+
+static int ft_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int HD, bool PAGED>
+static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* block_table,
+                     int table_width, int ring_pages, const int* cu_seqlens, const int* start_pos, int n_seqs,
+                     int n_tokens, int window, float scale, bf16* out, int nh, int nkv, int* status,
+                     cudaStream_t stream) {
+    constexpr int SMEM = (HD / 64) * FT_SUB_BYTES * 5 + 2 * FT_SUB_BYTES + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD, PAGED>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const dim3 grid((n_tokens + FT_BM - 1) / FT_BM + n_seqs, nh);
+    flash_prefill_tc_kernel<HD, PAGED><<<grid, FT_THREADS, SMEM, stream>>>(
+        mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, start_pos, n_seqs, window,
+        scale * 1.4426950408889634f, out, nh, nkv, status);
+    return tq_launch_status();
+}
+
+// q, out [T, nh * hd] bfloat16.  Keys/values: packed [T, nkv * hd] (every
+// sequence then starts at position 0 in this step) or pages
+// [n_pages, nkv, 64, hd].  Returns cudaErrorNotSupported (801) for head sizes
+// other than 64 and 128 or pages that are not 64 tokens.
+TQ_API int tq_flash_prefill_tc(const void* q, const void* k_packed, const void* v_packed, const void* k_pages,
+                               const void* v_pages, long long n_pages, const int* block_table, int table_width,
+                               int ring_pages, int page_tokens, const int* cu_seqlens, const int* start_pos, int n_seqs,
+                               int n_tokens, int window, float scale, void* out, int nh, int nkv, int hd, int* status,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || nh > 65535 || (hd != 64 && hd != 128)) return (int)cudaErrorNotSupported;
+    const bool paged = k_packed == nullptr;
+    if (paged && (page_tokens != 64 || !k_pages || !v_pages || !block_table)) return (int)cudaErrorNotSupported;
+    CUtensorMap mq, mk, mv;
+    int st = ft_map(&mq, q, (uint64_t)n_tokens, (uint64_t)nh * hd, (uint64_t)nh * hd, FT_BM);
+    if (st) return st;
+    if (paged) {
+        st = ft_map(&mk, k_pages, (uint64_t)n_pages * nkv * 64, (uint64_t)hd, (uint64_t)hd, 64);
+        if (!st) st = ft_map(&mv, v_pages, (uint64_t)n_pages * nkv * 64, (uint64_t)hd, (uint64_t)hd, 64);
+    } else {
+        st = ft_map(&mk, k_packed, (uint64_t)n_tokens, (uint64_t)nkv * hd, (uint64_t)nkv * hd, FT_BN);
+        if (!st) st = ft_map(&mv, v_packed, (uint64_t)n_tokens, (uint64_t)nkv * hd, (uint64_t)nkv * hd, FT_BN);
+    }
+    if (st) return st;
+#define TQ_FT(H, P) return ft_launch<H, P>(mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, start_pos, \
+                                           n_seqs, n_tokens, window, scale, (bf16*)out, nh, nkv, status, stream)
+    if (hd == 128 && paged) TQ_FT(128, true);
+    if (hd == 128 && !paged) TQ_FT(128, false);
+    if (hd == 64 && paged) TQ_FT(64, true);
+    TQ_FT(64, false);
+#undef TQ_FT
+}
