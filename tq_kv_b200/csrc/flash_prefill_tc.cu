@@ -3,7 +3,9 @@
 // A block owns 128 consecutive query tokens of one (sequence, q head) and walks
 // the keys in tiles of 128.  Per tile:
 //   S  = Q · K^T      tcgen05.mma, Q and K tiles K-major in shared memory (TMA,
-//                     128-byte swizzle), S[128 x 128] float32 in TMEM;
+//                     128-byte swizzle), S[128 x 128] float32 in TMEM (two
+//                     buffers: the next tile's product is issued while this
+//                     tile's softmax runs);
 //   softmax           four warps, one query row per thread (TMEM lane = row, so
 //                     the row maximum and sum need no shuffles), float32, with a
 //                     running maximum; P is written to shared memory as bfloat16
@@ -13,7 +15,7 @@
 //   O  = O * c + PV   in registers (one row of head_dim floats per thread).
 // Roles: warp 0 lane 0 issues TMA loads (Q once, K/V tiles through two stages),
 // warp 1 lane 0 issues the MMAs, warps 2..5 do softmax, accumulation and the
-// final store.  Keys and values come from the step's packed rows (PAGED =
+// final store.  Blocks with the most key tiles start first.  Keys and values come from the step's packed rows (PAGED =
 // false) or from the paged cache (two 64-token pages per tile).  An optional
 // sliding window narrows the key range; tiles outside a block's range are
 // never loaded.  All mbarrier waits are bounded (see gemm_tc.cu).
@@ -40,7 +42,7 @@ __device__ __forceinline__ bool ft_wait(uint32_t bar, uint32_t parity, bool back
             "selp.u32 %0, 1, 0, p;\n\t}\n"
             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
-        if (backoff) __nanosleep(100);
+        if (backoff) __nanosleep(20);
         if ((i & 255u) == 0 && clock64() - t0 > FT_WAIT_CYCLES) return false;
     }
 }
@@ -108,14 +110,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     uint64_t* q_full = bars;                               // 1
     uint64_t* kv_full = bars + 1;                          // [2]
     uint64_t* kv_empty = bars + 3;                         // [2]
-    uint64_t* s_full = bars + 5;
-    uint64_t* p_full = bars + 6;                           // 128 arrivals (softmax threads)
-    uint64_t* o_full = bars + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* s_full = bars + 5;                           // [2]
+    uint64_t* p_full = bars + 7;                           // 128 arrivals (softmax threads)
+    uint64_t* o_full = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile uint32_t* failed = tmem_slot + 1;
 
-    // which (sequence, 128-token tile) is this block's?
-    int b = -1, tile = blockIdx.x;
+    // which (sequence, 128-token tile) is this block's?  Later tiles of a sequence have more keys to walk:
+    // the grid is walked backwards, so that they start first.
+    int b = -1, tile = (int)gridDim.x - 1 - (int)blockIdx.x;
     for (int i = 0; i < n_seqs; ++i) {
         const int tiles = (cu_seqlens[i + 1] - cu_seqlens[i] + FT_BM - 1) / FT_BM;
         if (tile < tiles) { b = i; break; }
@@ -137,7 +140,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&kv_full[s])));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&kv_empty[s])));
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(s_full)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&s_full[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&s_full[1])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;\n" ::"r"(ft_smem(p_full)));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(o_full)));
         *failed = 0;
@@ -146,14 +150,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(ft_smem(tmem_slot)), "r"(256u) : "memory");
+                     ::"r"(ft_smem(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const uint32_t tmem_s = *tmem_slot;                    // S: columns 0..127
-    const uint32_t tmem_o = tmem_s + 128;                  // P·V of the current tile: columns 128..128+HD
+    const uint32_t tmem_s = *tmem_slot;                    // S: two buffers of 128 columns (the next tile's scores
+                                                           // are computed while this tile's softmax runs)
+    const uint32_t tmem_o = tmem_s + 256;                  // P·V of the current tile: columns 256..256+HD
 
     if (warp == 0) {
         if (lane == 0) {
@@ -197,20 +202,27 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                                      ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
             bool ok = ft_wait(ft_smem(q_full), 0);
             if (!ok) *failed = 1;
+            const uint32_t qa = ft_smem(q_s), pa = ft_smem(p_s);
+            auto issue_qk = [&](int it) -> bool {            // S[it & 1] = Q · K(it)^T over head_dim
+                const int s = it & 1;
+                if (!ft_wait(ft_smem(&kv_full[s]), (it >> 1) & 1)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t ka = ft_smem(k_s + s * TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * FT_SUB_BYTES + (ks & 3) * 32;
+                    ft_mma(tmem_s + s * FT_BN, ft_desc_k(qa + off), ft_desc_k(ka + off), idesc_s, ks > 0 ? 1u : 0u);
+                }
+                ft_commit(ft_smem(&s_full[s]));
+                return true;
+            };
+            if (ok && !issue_qk(0)) { *failed = 1; ok = false; }
             for (int it = 0; it < n_tiles && ok; ++it) {
                 const int s = it & 1;
-                if (!ft_wait(ft_smem(&kv_full[s]), (it >> 1) & 1)) { *failed = 1; ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t qa = ft_smem(q_s), ka = ft_smem(k_s + s * TILE_BYTES), va = ft_smem(v_s + s * TILE_BYTES);
-#pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {       // S = Q · K^T over head_dim
-                    const uint32_t off = (ks >> 2) * FT_SUB_BYTES + (ks & 3) * 32;
-                    ft_mma(tmem_s, ft_desc_k(qa + off), ft_desc_k(ka + off), idesc_s, ks > 0 ? 1u : 0u);
-                }
-                ft_commit(ft_smem(s_full));
+                if (it + 1 < n_tiles && !issue_qk(it + 1)) { *failed = 1; ok = false; break; }
                 if (!ft_wait(ft_smem(p_full), it & 1)) { *failed = 1; ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t pa = ft_smem(p_s);
+                const uint32_t va = ft_smem(v_s + s * TILE_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < FT_BN / 16; ++ks) {    // P·V over the tile's 128 keys
                     const uint32_t a_off = (ks >> 2) * FT_SUB_BYTES + (ks & 3) * 32;
@@ -234,19 +246,26 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         bool ok = true;
         for (int it = 0; it < n_tiles && ok; ++it) {
             const int j0 = j_begin + it * FT_BN;
-            if (!ft_wait(ft_smem(s_full), it & 1, true)) { *failed = 1; ok = false; break; }
+            if (!ft_wait(ft_smem(&s_full[it & 1]), (it >> 1) & 1, true)) { *failed = 1; ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            // key j is seen iff p_row - window < j <= p_row
+            const uint32_t s_addr = tmem_s + (it & 1) * FT_BN + lane_addr;
+            // key j is seen iff p_row - window < j <= p_row; most tiles lie inside every row's range
             const int j_hi = p_row, j_lo = window > 0 ? p_row - window + 1 : 0;
+            const bool inside = j0 + FT_BN - 1 <= p_first && (window <= 0 || j0 > p_last - window);
             float mx = -INFINITY;
 #pragma unroll 1
             for (int c = 0; c < FT_BN; c += 32) {
                 float v[32];
-                ft_ld32(tmem_s + lane_addr + c, v);
+                ft_ld32(s_addr + c, v);
+                if (inside) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int key = j0 + c + j;
-                    if (key >= j_lo && key <= j_hi) mx = fmaxf(mx, v[j]);
+                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int key = j0 + c + j;
+                        if (key >= j_lo && key <= j_hi) mx = fmaxf(mx, v[j]);
+                    }
                 }
             }
             const float m_new = fmaxf(m_run, mx * scale_log2);
@@ -256,13 +275,19 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll 1
             for (int c = 0; c < FT_BN; c += 32) {
                 float v[32];
-                ft_ld32(tmem_s + lane_addr + c, v);
+                ft_ld32(s_addr + c, v);
                 uint32_t packed[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
                     const int key = j0 + c + j;
-                    float p0 = (key >= j_lo && key <= j_hi && m_new > -INFINITY) ? exp2f(v[j] * scale_log2 - m_new) : 0.f;
-                    float p1 = (key + 1 >= j_lo && key + 1 <= j_hi && m_new > -INFINITY) ? exp2f(v[j + 1] * scale_log2 - m_new) : 0.f;
+                    float p0, p1;
+                    if (inside) {
+                        p0 = exp2f(fmaf(v[j], scale_log2, -m_new));
+                        p1 = exp2f(fmaf(v[j + 1], scale_log2, -m_new));
+                    } else {
+                        p0 = (key >= j_lo && key <= j_hi && m_new > -INFINITY) ? exp2f(fmaf(v[j], scale_log2, -m_new)) : 0.f;
+                        p1 = (key + 1 >= j_lo && key + 1 <= j_hi && m_new > -INFINITY) ? exp2f(fmaf(v[j + 1], scale_log2, -m_new)) : 0.f;
+                    }
                     rs += p0 + p1;
                     __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                     packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
@@ -310,7 +335,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     __syncthreads();
     if (threadIdx.x == 0 && *failed && status) atomicOr(status, 4);
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(512u) : "memory");
     }
 }
 
