@@ -1,24 +1,32 @@
 // Causal grouped-query attention for prompts on the tcgen05 tensor cores.
 //
 // A block owns 128 consecutive query tokens of one (sequence, q head) and walks
-// the keys in tiles of 128.  Per tile:
+// the keys in tiles of 64.  Per tile:
 //   S  = Q · K^T      tcgen05.mma, Q and K tiles K-major in shared memory (TMA,
-//                     128-byte swizzle), S[128 x 128] float32 in TMEM (two
-//                     buffers: the next tile's product is issued while this
-//                     tile's softmax runs);
+//                     128-byte swizzle), S[128 x 64] float32 in TMEM; two S
+//                     buffers, so the next tile's product is issued while this
+//                     tile's softmax runs;
 //   softmax           four warps, one query row per thread (TMEM lane = row, so
-//                     the row maximum and sum need no shuffles), float32, with a
-//                     running maximum; P is written to shared memory as bfloat16
-//                     in the swizzled K-major layout the next MMA reads;
-//   PV = P · V        tcgen05.mma with V as an MN-major operand (the V tile is
-//                     [keys][head_dim] as it lies in memory), result in TMEM;
-//   O  = O * c + PV   in registers (one row of head_dim floats per thread).
+//                     the row maximum and sum need no shuffles), float32; P is
+//                     written to shared memory as bfloat16 in the swizzled
+//                     K-major layout the next MMA reads;
+//   O += P · V        tcgen05.mma with V as an MN-major operand (the V tile is
+//                     [keys][head_dim] as it lies in memory), accumulated in TMEM
+//                     over all tiles and read once at the end.
+// P and O are scaled against a reference maximum per row that moves only when
+// the row's maximum has grown by more than 2^8; then the warp multiplies its
+// rows of O in TMEM (tcgen05.ld / st) and the running sums by the same factor.
+// The result is the same softmax (any reference gives the same quotient); the
+// exponentials stay below 2^8.
 // Roles: warp 0 lane 0 issues TMA loads (Q once, K/V tiles through two stages),
-// warp 1 lane 0 issues the MMAs, warps 2..5 do softmax, accumulation and the
-// final store.  Blocks with the most key tiles start first.  Keys and values come from the step's packed rows (PAGED =
-// false) or from the paged cache (two 64-token pages per tile).  An optional
-// sliding window narrows the key range; tiles outside a block's range are
-// never loaded.  All mbarrier waits are bounded (see gemm_tc.cu).
+// warp 1 lane 0 issues the MMAs, warps 2..5 do the softmax and the final store.
+// A block takes half an SM's shared memory and half its TMEM: two blocks share
+// an SM, and one's tensor-core work runs under the other's softmax.  Blocks
+// with the most key tiles start first.  Keys and values come from the step's
+// packed rows (PAGED = false) or from the paged cache (one 64-token page per
+// tile).  An optional sliding window narrows the key range; tiles outside a
+// block's range are never loaded.  All mbarrier waits are bounded (see
+// gemm_tc.cu).
 //
 // Formulas: src/models/turbo_generic.rs:1620-1631 (see attention.cu).
 #include <cuda.h>
@@ -26,9 +34,10 @@
 #include "common.cuh"
 
 #define FT_BM 128
-#define FT_BN 128
+#define FT_BN 64
 #define FT_THREADS 192
-#define FT_SUB_BYTES (128 * 128)          // a [128 rows x 64 bf16] sub-tile
+#define FT_SUB_BYTES (128 * 128)          // a [128 rows x 64 bf16] sub-tile (Q, P)
+#define FT_KV_SUB_BYTES (FT_BN * 128)     // a [64 keys x 64 bf16] sub-tile (K, V)
 #define FT_WAIT_CYCLES (4000000000ll)
 
 __device__ __forceinline__ uint32_t ft_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -80,6 +89,38 @@ __device__ __forceinline__ void ft_ld32(uint32_t taddr, float* v) {
         : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void ft_ld32_issue(uint32_t taddr, float* v) {   // the caller waits (ft_ld_wait)
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void ft_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+// 2^x of the special-function unit (2 ulp; 2^-inf = 0): the probabilities are rounded to bfloat16 anyway
+__device__ __forceinline__ float ft_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void ft_st32(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
 // K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t ft_desc_k(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
@@ -92,28 +133,36 @@ __device__ __forceinline__ uint64_t ft_desc_mn(uint32_t saddr, uint32_t mn_strid
 }
 
 template <int HD, bool PAGED>
-__global__ void __launch_bounds__(FT_THREADS, 1)
+__global__ void __launch_bounds__(FT_THREADS, 2)
 flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
                         int ring_pages, const int* __restrict__ cu_seqlens, const int* __restrict__ start_pos,
                         int n_seqs, int window, float scale_log2, bf16* __restrict__ out, int nh, int nkv,
                         int* __restrict__ status) {
     constexpr int SUBS = HD / 64;                          // 64-column sub-tiles of a Q, K or V tile
-    constexpr int TILE_BYTES = SUBS * FT_SUB_BYTES;
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_s = base;
-    unsigned char* k_s = q_s + TILE_BYTES;                 // [2 stages]
-    unsigned char* v_s = k_s + 2 * TILE_BYTES;             // [2 stages]
-    unsigned char* p_s = v_s + 2 * TILE_BYTES;             // P: two sub-tiles of 64 keys
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * FT_SUB_BYTES);
-    uint64_t* q_full = bars;                               // 1
-    uint64_t* kv_full = bars + 1;                          // [2]
-    uint64_t* kv_empty = bars + 3;                         // [2]
-    uint64_t* s_full = bars + 5;                           // [2]
-    uint64_t* p_full = bars + 7;                           // 128 arrivals (softmax threads)
-    uint64_t* o_full = bars + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    constexpr int Q_BYTES = SUBS * FT_SUB_BYTES;
+    constexpr int KV_BYTES = SUBS * FT_KV_SUB_BYTES;       // a K or V tile of 64 keys
+    // 1024-byte alignment (the swizzle's period) is asked of the launch, not bought with slack: two blocks
+    // must fit an SM.  A base that is not aligned all the same is reported through *status, nothing runs.
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    if (reinterpret_cast<uintptr_t>(smem_raw) & 1023) {
+        if (threadIdx.x == 0 && status) atomicOr(status, 8);
+        return;
+    }
+    unsigned char* q_s = smem_raw;
+    unsigned char* k_s = q_s + Q_BYTES;                    // [2 stages]
+    unsigned char* v_s = k_s + 2 * KV_BYTES;               // [2 stages]
+    unsigned char* p_s = v_s + 2 * KV_BYTES;               // P: [128 rows x 64 keys]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + FT_SUB_BYTES);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;                           // [2]  K and V have rings of their own: a K stage is
+    uint64_t* k_empty = bars + 3;                          // [2]  free as soon as its Q·K^T is done, long before
+    uint64_t* v_full = bars + 5;                           // [2]  the tile's P·V, so the load of the tile after
+    uint64_t* v_empty = bars + 7;                          // [2]  next has a whole iteration to arrive
+    uint64_t* s_full = bars + 9;                           // [2]
+    uint64_t* p_full = bars + 11;                          // 128 arrivals (softmax threads)
+    uint64_t* p_empty = bars + 12;                         // the P·V of a tile is done: P and O may be touched
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile uint32_t* failed = tmem_slot + 1;
 
     // which (sequence, 128-token tile) is this block's?  Later tiles of a sequence have more keys to walk:
@@ -137,61 +186,57 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(q_full)));
         for (int s = 0; s < 2; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&kv_full[s])));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&kv_empty[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&k_full[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&k_empty[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&v_full[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&v_empty[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&s_full[s])));
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&s_full[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(&s_full[1])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;\n" ::"r"(ft_smem(p_full)));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(o_full)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(p_empty)));
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(ft_smem(tmem_slot)), "r"(512u) : "memory");
+                     ::"r"(ft_smem(tmem_slot)), "r"(256u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const uint32_t tmem_s = *tmem_slot;                    // S: two buffers of 128 columns (the next tile's scores
-                                                           // are computed while this tile's softmax runs)
-    const uint32_t tmem_o = tmem_s + 256;                  // P·V of the current tile: columns 256..256+HD
+    const uint32_t tmem_s = *tmem_slot;                    // S: two buffers of 64 columns
+    const uint32_t tmem_o = tmem_s + 128;                  // O: columns 128..128+HD, accumulated over the tiles
 
     if (warp == 0) {
         if (lane == 0) {
             // ---- producer ----
-            ft_expect(ft_smem(q_full), TILE_BYTES);
+            ft_expect(ft_smem(q_full), Q_BYTES);
             for (int sub = 0; sub < SUBS; ++sub)
                 ft_tma(ft_smem(q_s + sub * FT_SUB_BYTES), &map_q, h * HD + sub * 64, tok0 + tile * FT_BM, ft_smem(q_full));
             for (int it = 0; it < n_tiles; ++it) {
                 const int s = it & 1;
-                if (!ft_wait(ft_smem(&kv_empty[s]), ((it >> 1) & 1) ^ 1)) { *failed = 1; break; }
-                const uint32_t fb = ft_smem(&kv_full[s]);
-                ft_expect(fb, 2 * TILE_BYTES);
                 const int j0 = j_begin + it * FT_BN;
+                int row;
                 if (PAGED) {
-                    for (int half = 0; half < 2; ++half) {
-                        int lp = (j0 + 64 * half) / 64;
-                        if (ring_pages > 0) lp %= ring_pages;
-                        // pages past the sequence's last one are not in the table: any valid page will do (masked)
-                        const int last_lp = ring_pages > 0 ? (p_last / 64) % ring_pages : p_last / 64;
-                        if (j0 + 64 * half > p_last) lp = last_lp;
-                        const int row = (block_table[(size_t)b * table_width + lp] * nkv + g) * 64;
-                        for (int sub = 0; sub < SUBS; ++sub) {
-                            ft_tma(ft_smem(k_s + s * TILE_BYTES + sub * FT_SUB_BYTES + half * 8192), &map_k, sub * 64, row, fb);
-                            ft_tma(ft_smem(v_s + s * TILE_BYTES + sub * FT_SUB_BYTES + half * 8192), &map_v, sub * 64, row, fb);
-                        }
-                    }
+                    int lp = j0 / 64;
+                    if (ring_pages > 0) lp %= ring_pages;
+                    row = (block_table[(size_t)b * table_width + lp] * nkv + g) * 64;
                 } else {
-                    const int row = tok0 - start + j0;       // key j lives at packed token tok0 - start + j
-                    for (int sub = 0; sub < SUBS; ++sub) {
-                        ft_tma(ft_smem(k_s + s * TILE_BYTES + sub * FT_SUB_BYTES), &map_k, g * HD + sub * 64, row, fb);
-                        ft_tma(ft_smem(v_s + s * TILE_BYTES + sub * FT_SUB_BYTES), &map_v, g * HD + sub * 64, row, fb);
-                    }
+                    row = tok0 - start + j0;                 // key j lives at packed token tok0 - start + j
                 }
+                const int col = PAGED ? 0 : g * HD;
+                if (!ft_wait(ft_smem(&k_empty[s]), ((it >> 1) & 1) ^ 1)) { *failed = 1; break; }
+                ft_expect(ft_smem(&k_full[s]), KV_BYTES);
+                for (int sub = 0; sub < SUBS; ++sub)
+                    ft_tma(ft_smem(k_s + s * KV_BYTES + sub * FT_KV_SUB_BYTES), &map_k, col + sub * 64, row,
+                           ft_smem(&k_full[s]));
+                if (!ft_wait(ft_smem(&v_empty[s]), ((it >> 1) & 1) ^ 1)) { *failed = 1; break; }
+                ft_expect(ft_smem(&v_full[s]), KV_BYTES);
+                for (int sub = 0; sub < SUBS; ++sub)
+                    ft_tma(ft_smem(v_s + s * KV_BYTES + sub * FT_KV_SUB_BYTES), &map_v, col + sub * 64, row,
+                           ft_smem(&v_full[s]));
             }
         }
     } else if (warp == 1) {
@@ -205,44 +250,45 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const uint32_t qa = ft_smem(q_s), pa = ft_smem(p_s);
             auto issue_qk = [&](int it) -> bool {            // S[it & 1] = Q · K(it)^T over head_dim
                 const int s = it & 1;
-                if (!ft_wait(ft_smem(&kv_full[s]), (it >> 1) & 1)) return false;
+                if (!ft_wait(ft_smem(&k_full[s]), (it >> 1) & 1)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t ka = ft_smem(k_s + s * TILE_BYTES);
+                const uint32_t ka = ft_smem(k_s + s * KV_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * FT_SUB_BYTES + (ks & 3) * 32;
-                    ft_mma(tmem_s + s * FT_BN, ft_desc_k(qa + off), ft_desc_k(ka + off), idesc_s, ks > 0 ? 1u : 0u);
-                }
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    ft_mma(tmem_s + s * FT_BN, ft_desc_k(qa + (ks >> 2) * FT_SUB_BYTES + (ks & 3) * 32),
+                           ft_desc_k(ka + (ks >> 2) * FT_KV_SUB_BYTES + (ks & 3) * 32), idesc_s, ks > 0 ? 1u : 0u);
+                ft_commit(ft_smem(&k_empty[s]));
                 ft_commit(ft_smem(&s_full[s]));
                 return true;
             };
             if (ok && !issue_qk(0)) { *failed = 1; ok = false; }
             for (int it = 0; it < n_tiles && ok; ++it) {
                 const int s = it & 1;
+                // the next tile's scores are computed while the softmax threads work on this one
                 if (it + 1 < n_tiles && !issue_qk(it + 1)) { *failed = 1; ok = false; break; }
-                if (!ft_wait(ft_smem(p_full), it & 1)) { *failed = 1; ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t va = ft_smem(v_s + s * TILE_BYTES);
-#pragma unroll
-                for (int ks = 0; ks < FT_BN / 16; ++ks) {    // P·V over the tile's 128 keys
-                    const uint32_t a_off = (ks >> 2) * FT_SUB_BYTES + (ks & 3) * 32;
-                    ft_mma(tmem_o, ft_desc_k(pa + a_off), ft_desc_mn(va + ks * 2048, FT_SUB_BYTES), idesc_o, ks > 0 ? 1u : 0u);
+                if (!ft_wait(ft_smem(&v_full[s]), (it >> 1) & 1) || !ft_wait(ft_smem(p_full), it & 1)) {
+                    *failed = 1; ok = false; break;
                 }
-                ft_commit(ft_smem(&kv_empty[s]));            // the stage is free once these MMAs are done
-                ft_commit(ft_smem(o_full));
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t va = ft_smem(v_s + s * KV_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < FT_BN / 16; ++ks)      // O += P · V over the tile's 64 keys
+                    ft_mma(tmem_o, ft_desc_k(pa + ks * 32), ft_desc_mn(va + ks * 2048, FT_KV_SUB_BYTES), idesc_o,
+                           (it > 0 || ks > 0) ? 1u : 0u);
+                ft_commit(ft_smem(&v_empty[s]));             // the stage is free once these MMAs are done
+                ft_commit(ft_smem(p_empty));
             }
         }
     } else {
-        // ---- softmax, accumulation, store: thread = query row ----
+        // ---- softmax and the final store: thread = query row.  O stays in TMEM; it is accumulated against a
+        // reference maximum that only moves when a row's maximum has grown by more than 2^8, in which case the
+        // warp rescales its rows of O (and the running sums) — rare after the first tiles. ----
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                   // row of the tile = TMEM lane
         const int i_row = tile * FT_BM + r;                  // token index within the sequence
         const int p_row = start + min(i_row, len - 1);       // rows past the end repeat the last row (never stored)
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        float m_run = -INFINITY, l_run = 0.f;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int it = 0; it < n_tiles && ok; ++it) {
             const int j0 = j_begin + it * FT_BN;
@@ -252,81 +298,86 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             // key j is seen iff p_row - window < j <= p_row; most tiles lie inside every row's range
             const int j_hi = p_row, j_lo = window > 0 ? p_row - window + 1 : 0;
             const bool inside = j0 + FT_BN - 1 <= p_first && (window <= 0 || j0 > p_last - window);
+            float sv[FT_BN];                                  // the row's scores of this tile
+#pragma unroll
+            for (int c = 0; c < FT_BN; c += 32) ft_ld32_issue(s_addr + c, sv + c);
+            ft_ld_wait();
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < FT_BN; c += 32) {
-                float v[32];
-                ft_ld32(s_addr + c, v);
-                if (inside) {
+            if (inside) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[j]);
-                } else {
+                for (int j = 0; j < FT_BN; ++j) mx = fmaxf(mx, sv[j]);
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int key = j0 + c + j;
-                        if (key >= j_lo && key <= j_hi) mx = fmaxf(mx, v[j]);
-                    }
+                for (int j = 0; j < FT_BN; ++j) {
+                    const int key = j0 + j;
+                    if (key >= j_lo && key <= j_hi) mx = fmaxf(mx, sv[j]);
+                    else sv[j] = -INFINITY;                    // a masked key: 2^-inf = 0 below
                 }
             }
-            const float m_new = fmaxf(m_run, mx * scale_log2);
-            const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
-            m_run = m_new;
-            float rs = 0.f;
+            const float m_tile = mx * scale_log2;
+            // P of the tile before and O are in use until that tile's P·V is done
+            if (it > 0 && !ft_wait(ft_smem(p_empty), (it - 1) & 1, true)) { *failed = 1; ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const bool grow = m_tile > m_ref + 8.f;          // also true for the first finite maximum
+            if (__any_sync(0xffffffffu, grow) && it > 0) {
+                const float f = grow ? exp2f(m_ref - m_tile) : 1.f;      // exp2(-inf) = 0: nothing was summed yet
 #pragma unroll 1
-            for (int c = 0; c < FT_BN; c += 32) {
-                float v[32];
-                ft_ld32(s_addr + c, v);
-                uint32_t packed[16];
+                for (int c = 0; c < HD; c += 32) {
+                    float v[32];
+                    ft_ld32(tmem_o + lane_addr + c, v);
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int key = j0 + c + j;
-                    float p0, p1;
-                    if (inside) {
-                        p0 = exp2f(fmaf(v[j], scale_log2, -m_new));
-                        p1 = exp2f(fmaf(v[j + 1], scale_log2, -m_new));
-                    } else {
-                        p0 = (key >= j_lo && key <= j_hi && m_new > -INFINITY) ? exp2f(fmaf(v[j], scale_log2, -m_new)) : 0.f;
-                        p1 = (key + 1 >= j_lo && key + 1 <= j_hi && m_new > -INFINITY) ? exp2f(fmaf(v[j + 1], scale_log2, -m_new)) : 0.f;
-                    }
+                    for (int j = 0; j < 32; ++j) v[j] *= f;
+                    ft_st32(tmem_o + lane_addr + c, v);
+                }
+                l_run *= f;
+            }
+            if (grow) m_ref = m_tile;
+            // a row that has seen no key yet keeps m_ref = -inf; its scores are all masked (-inf) and must
+            // give 0, not 2^(-inf + inf)
+            const float neg_ref = m_ref > -INFINITY ? -m_ref : 0.f;
+            float rs = 0.f;
+            unsigned char* prow = p_s + r * 128;
+#pragma unroll
+            for (int c = 0; c < FT_BN; c += 8) {              // 8 keys = one 16-byte chunk of the swizzled row
+                uint32_t packed[4];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float p0 = ft_exp2(fmaf(sv[c + j], scale_log2, neg_ref));
+                    const float p1 = ft_exp2(fmaf(sv[c + j + 1], scale_log2, neg_ref));
                     rs += p0 + p1;
                     __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                     packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
                 }
-                // 32 keys = four 16-byte chunks of this row, in the swizzled K-major layout
-                unsigned char* prow = p_s + (c >> 6) * FT_SUB_BYTES + r * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c & 63) >> 3) + q4;
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
+                *reinterpret_cast<uint4*>(prow + (((c >> 3) ^ (r & 7)) << 4)) =
+                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            l_run = l_run * corr + rs;
+            l_run += rs;
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P is read by the tensor core
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             ft_arrive(ft_smem(p_full));
-            if (!ft_wait(ft_smem(o_full), it & 1, true)) { *failed = 1; ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
+        }
+        // the last tile's P·V, then O / l
+        if (ok && !ft_wait(ft_smem(p_empty), (n_tiles - 1) & 1, true)) { *failed = 1; ok = false; }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        if (ok) {
+            const float inv = 1.f / l_run;
+            bf16* orow = out + ((size_t)(tok0 + min(i_row, len - 1)) * nh + h) * HD;
+#pragma unroll 1
             for (int c = 0; c < HD; c += 32) {
                 float v[32];
-                ft_ld32(tmem_o + lane_addr + c, v);
+                ft_ld32(tmem_o + lane_addr + c, v);           // (all lanes take part in the load)
+                if (i_row < len) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * corr + v[j];
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        }
-        if (ok && i_row < len) {
-            const float inv = 1.f / l_run;
-            bf16* orow = out + ((size_t)(tok0 + i_row) * nh + h) * HD;
-#pragma unroll
-            for (int d = 0; d < HD; d += 8) {
-                __nv_bfloat162 a = __floats2bfloat162_rn(o[d] * inv, o[d + 1] * inv);
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(o[d + 2] * inv, o[d + 3] * inv);
-                __nv_bfloat162 c2 = __floats2bfloat162_rn(o[d + 4] * inv, o[d + 5] * inv);
-                __nv_bfloat162 d2 = __floats2bfloat162_rn(o[d + 6] * inv, o[d + 7] * inv);
-                *reinterpret_cast<uint4*>(orow + d) = make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b2),
-                                                                 *reinterpret_cast<uint32_t*>(&c2), *reinterpret_cast<uint32_t*>(&d2));
+                    for (int d = 0; d < 32; d += 8) {
+                        __nv_bfloat162 a = __floats2bfloat162_rn(v[d] * inv, v[d + 1] * inv);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(v[d + 2] * inv, v[d + 3] * inv);
+                        __nv_bfloat162 c2 = __floats2bfloat162_rn(v[d + 4] * inv, v[d + 5] * inv);
+                        __nv_bfloat162 d2 = __floats2bfloat162_rn(v[d + 6] * inv, v[d + 7] * inv);
+                        *reinterpret_cast<uint4*>(orow + c + d) =
+                            make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b2),
+                                       *reinterpret_cast<uint32_t*>(&c2), *reinterpret_cast<uint32_t*>(&d2));
+                    }
+                }
             }
         }
     }
@@ -335,7 +386,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     __syncthreads();
     if (threadIdx.x == 0 && *failed && status) atomicOr(status, 4);
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(256u) : "memory");
     }
 }
 
@@ -355,7 +406,7 @@ static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
                      int table_width, int ring_pages, const int* cu_seqlens, const int* start_pos, int n_seqs,
                      int n_tokens, int window, float scale, bf16* out, int nh, int nkv, int* status,
                      cudaStream_t stream) {
-    constexpr int SMEM = (HD / 64) * FT_SUB_BYTES * 5 + 2 * FT_SUB_BYTES + 1024 + 256;
+    constexpr int SMEM = (HD / 64) * (FT_SUB_BYTES + 4 * FT_KV_SUB_BYTES) + FT_SUB_BYTES + 256;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD, PAGED>,
