@@ -15,8 +15,9 @@
 //
 // Roles: warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the MMAs
 // (warp 1 also allocates and frees TMEM), warps 2..5 run the epilogue of one
-// accumulator while the MMAs fill the other (warp w reads TMEM lanes
-// 32 (w % 4) .. +31, transposes through shared memory and writes whole rows).
+// accumulator while the MMAs fill the other: warp w reads TMEM lanes
+// 32 (w % 4) .. +31, lays [32 x 32] pieces into shared memory and hands them
+// to TMA, as a store or, for the residual sum, as a reduce-add done in the L2.
 // Every wait on an mbarrier is bounded: when a bound is hit the role raises
 // a flag, stops, the others run into their own bounds, the block still frees
 // its TMEM, raises a bit in *status and returns: an error, not a hang.
@@ -37,7 +38,8 @@
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_B_BYTES (TC_BN * TC_BK * 2)
 #define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
-#define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 4 * 32 * 33 * 4 /* epilogue */ + 256)
+#define TC_EPI_BYTES (32 * 32 * 4)        /* a warp's [32 rows x 32 columns] float32 piece on its way out */
+#define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 4 * 2 * TC_EPI_BYTES + 256)
 #define TC_WAIT_CYCLES (4000000000ll)     /* about two seconds of SM clock */
 
 #define EPI_STORE 0
@@ -132,13 +134,13 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t m, uint32_t n) {
 template <int EPI, typename TO>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const float* __restrict__ bias, TO* __restrict__ C, int M, int N, int K, int ldc, int b_rows_second,
-               int n_whole, int parts, int* __restrict__ status) {
+               const __grid_constant__ CUtensorMap map_c, const float* __restrict__ bias, int M, int N, int K,
+               int b_rows_second, int n_whole, int parts, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    float* staging = reinterpret_cast<float*>(tiles + TC_STAGES * TC_STAGE_BYTES);       // [4 warps][32][33]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 4 * 32 * 33);
+    unsigned char* staging = tiles + TC_STAGES * TC_STAGE_BYTES;       // [4 warps][2 buffers][32 rows][128 bytes]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 4 * 2 * TC_EPI_BYTES);
     // bars: full[S], empty[S], acc_full[2], acc_empty[2]; then the TMEM address and a failure flag
     uint64_t* full = bars;
     uint64_t* empty = bars + TC_STAGES;
@@ -248,10 +250,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else {
-        // ---- epilogue warps: warp w reads TMEM lanes 32 * (w % 4) .. + 31 = rows of the tile ----
+        // ---- epilogue warps: warp w reads TMEM lanes 32 * (w % 4) .. + 31 = rows of the tile.  A thread holds
+        // 32 neighbouring columns of its row; the warp lays its [32 x 32] piece into shared memory (rows of 128
+        // bytes, 16-byte chunks swizzled so that the 32 rows do not meet in a bank) and one lane hands it to
+        // TMA: a store, or for the residual sum a reduce-add, which adds in the L2 without reading C into the
+        // SM and is the same operation for whole tiles and for shares of K.  TMA clips rows >= M and columns
+        // >= N.  Two buffers per warp: a piece is written while the one before is on its way. ----
         const int quarter = warp & 3;
-        float* st = staging + (warp - 2) * 32 * 33;
-        uint32_t local = 0;
+        unsigned char* st = staging + (warp - 2) * 2 * TC_EPI_BYTES;
+        constexpr int ROW_BYTES = 32 * (int)sizeof(TO);       // 128 (float32) or 64 (bfloat16)
+        uint32_t local = 0, piece = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
             int t, k_lo, k_iters, part;
@@ -262,8 +270,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC_BN;
             const int row0 = m0 + quarter * 32;
+            const bool rows_live = row0 < M;                  // a warp whose rows all lie past M stores nothing
 #pragma unroll 1
             for (int c = 0; c < OUT_COLS; c += 32) {
+                if (n0 + c >= N) break;
                 float v[32];
                 if (EPI == EPI_SWIGLU) {
                     float u[32];
@@ -276,55 +286,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tc_ld32(t_row + c, v);
                     tc_wait_ld();
                 }
-                // transpose through shared memory: thread = row  ->  thread = column, rows one after another
+                if (bias != nullptr && part <= 0) {           // one share of a tile adds the bias
+                    const int col = n0 + c + lane;
+                    const float mine = col < N ? bias[col] : 0.f;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) st[lane * 33 + j] = v[j];
+                    for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
+                }
+                if (!rows_live) continue;
+                unsigned char* pb = st + (piece & 1) * TC_EPI_BYTES;
+                // the piece before last used this buffer: its bytes must have been read
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
                 __syncwarp();
-                const int col = n0 + c + lane;
-                const float bv = (bias && col < N && part <= 0) ? bias[col] : 0.f;   // one share adds the bias
-                if (sizeof(TO) == 4 || EPI == EPI_ACCUM) {
-                    if (col < N) {
-                        const int rows = min(32, M - row0);
-                        TO* out = C + (size_t)row0 * ldc + col;
-                        if (EPI == EPI_ACCUM && part >= 0) {
-                            // a share of K: several blocks add into this tile, in whatever order they arrive
-                            for (int r = 0; r < rows; ++r)
-                                atomicAdd(reinterpret_cast<float*>(out) + (size_t)r * ldc, st[r * 33 + lane] + bv);
-                        } else if (EPI == EPI_ACCUM) {
-                            // all old values first (independent loads in flight), then the sums
-                            float old[32];
+                if (sizeof(TO) == 4) {
 #pragma unroll
-                            for (int r = 0; r < 32; ++r) old[r] = r < rows ? to_f32<TO>(out[(size_t)r * ldc]) : 0.f;
-#pragma unroll
-                            for (int r = 0; r < 32; ++r)
-                                if (r < rows) out[(size_t)r * ldc] = from_f32<TO>(st[r * 33 + lane] + bv + old[r]);
-                        } else {
-#pragma unroll 8
-                            for (int r = 0; r < rows; ++r) out[(size_t)r * ldc] = from_f32<TO>(st[r * 33 + lane] + bv);
-                        }
-                    }
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(pb + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 } else {
-                    // 16-bit output: a lane writes two neighbouring columns, the warp two rows at a time
-                    const int cp = 2 * (lane & 15), half = lane >> 4;
-                    const int col2 = n0 + c + cp;
-                    const float b0 = (bias && col2 < N) ? bias[col2] : 0.f;
-                    const float b1 = (bias && col2 + 1 < N) ? bias[col2 + 1] : 0.f;
-                    for (int r = half; r < 32; r += 2) {
-                        if (row0 + r >= M) break;
-                        TO* out = C + (size_t)(row0 + r) * ldc + col2;
-                        const float x0 = st[r * 33 + cp] + b0, x1 = st[r * 33 + cp + 1] + b1;
-                        if (col2 + 1 < N && (reinterpret_cast<uintptr_t>(out) & 3) == 0) store2_f32<TO>(out, x0, x1);
-                        else {
-                            if (col2 < N) out[0] = from_f32<TO>(x0);
-                            if (col2 + 1 < N) out[1] = from_f32<TO>(x1);
-                        }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162 a = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                        __nv_bfloat162 c2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                        __nv_bfloat162 d2 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                        *reinterpret_cast<uint4*>(pb + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                            make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b2),
+                                       *reinterpret_cast<uint32_t*>(&c2), *reinterpret_cast<uint32_t*>(&d2));
                     }
                 }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 __syncwarp();
+                if (lane == 0) {
+                    if (EPI == EPI_ACCUM)
+                        asm volatile(
+                            "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];\n"
+                            ::"l"(&map_c), "r"(n0 + c), "r"(row0), "r"(smem_u32(pb)) : "memory");
+                    else
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];\n"
+                            ::"l"(&map_c), "r"(n0 + c), "r"(row0), "r"(smem_u32(pb)) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                }
+                ++piece;
             }
             tc_fence_before();
+            __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // all pieces have landed
+        (void)ROW_BYTES;
     }
     __syncwarp();
     tc_fence_before();
@@ -349,9 +359,23 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
+// C: rows x cols of float32 or bfloat16, row stride ld elements; box = 32 rows x 32 columns, swizzled over the
+// row's bytes (128 or 64) as the epilogue lays it out
+static int make_map_c(CUtensorMap* map, const void* base, bool f32, uint64_t rows, uint64_t cols, uint64_t ld) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * (f32 ? 4 : 2)};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = cuTensorMapEncodeTiled(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
 template <int EPI, typename TO>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const float* bias, void* C, int M, int N, int K,
-                     int ldc, int b_rows_second, int* status, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const float* bias, int M, int N,
+                     int K, int b_rows_second, int* status, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -382,14 +406,15 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const float* 
         }
         if (parts > 1) n_whole = n_tiles - rem;
     }
-    gemm_tc_kernel<EPI, TO><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(ma, mb, bias, (TO*)C, M, N, K, ldc,
-                                                                        b_rows_second, n_whole, parts, status);
+    gemm_tc_kernel<EPI, TO><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(ma, mb, mc, bias, M, N, K, b_rows_second,
+                                                                        n_whole, parts, status);
     return tq_launch_status();
 }
 
 // A [M, K] and B [N, K] (or [2N, K] with epilogue 2) bfloat16 with row strides
 // lda / ldb (elements, multiples of 8; bases 16-byte aligned); C [M, N] with
-// row stride ldc, float32 or bfloat16 (epilogue 1 needs float32).
+// row stride ldc (base and row stride in bytes multiples of 16), float32 or
+// bfloat16 (epilogue 1 needs float32).
 // status: device int, bit 1 is raised if a pipeline wait ran out.
 TQ_API int tq_gemm_tc(const void* A, const void* B, const float* bias, void* C, int c_dtype, int M, int N, int K,
                       int lda, int ldb, int ldc, int epilogue, int* status, cudaStream_t stream) {
@@ -398,6 +423,10 @@ TQ_API int tq_gemm_tc(const void* A, const void* B, const float* bias, void* C, 
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
         return (int)cudaErrorInvalidValue;
     if (epilogue == EPI_ACCUM && c_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    if (c_dtype != TQ_F32 && c_dtype != TQ_BF16) return (int)cudaErrorInvalidValue;
+    // C leaves through TMA: 16-byte aligned base and row stride
+    if ((reinterpret_cast<uintptr_t>(C) & 15) || ((size_t)ldc * (c_dtype == TQ_F32 ? 4 : 2)) % 16)
+        return (int)cudaErrorInvalidValue;
     if (epilogue == EPI_SWIGLU && (N & 1)) return (int)cudaErrorInvalidValue;
     CUtensorMap ma, mb;
     int st = make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM);
@@ -405,7 +434,10 @@ TQ_API int tq_gemm_tc(const void* A, const void* B, const float* bias, void* C, 
     const uint64_t b_rows = epilogue == EPI_SWIGLU ? 2ull * N : (uint64_t)N;
     st = make_map(&mb, B, b_rows, (uint64_t)K, (uint64_t)ldb, epilogue == EPI_SWIGLU ? TC_BN / 2 : TC_BN);
     if (st) return st;
-#define TQ_TC(E, T) return launch_tc<E, T>(ma, mb, bias, C, M, N, K, ldc, N, status, stream)
+    CUtensorMap mc;
+    st = make_map_c(&mc, C, c_dtype == TQ_F32, (uint64_t)M, (uint64_t)N, (uint64_t)ldc);
+    if (st) return st;
+#define TQ_TC(E, T) return launch_tc<E, T>(ma, mb, mc, bias, M, N, K, N, status, stream)
     if (epilogue == EPI_STORE && c_dtype == TQ_F32) TQ_TC(EPI_STORE, float);
     if (epilogue == EPI_STORE && c_dtype == TQ_BF16) TQ_TC(EPI_STORE, bf16);
     if (epilogue == EPI_ACCUM) TQ_TC(EPI_ACCUM, float);

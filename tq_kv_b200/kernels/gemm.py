@@ -95,7 +95,9 @@ def check_tc_status() -> None:
 def _tc_ok(x, w, out, swiglu) -> bool:
     return (USE_TCGEN05 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-            and (not swiglu or out.shape[1] % 2 == 0) and out.dtype in (torch.float32, torch.bfloat16))
+            and (not swiglu or out.shape[1] % 2 == 0) and out.dtype in (torch.float32, torch.bfloat16)
+            # the result leaves through TMA: 16-byte aligned base and row stride
+            and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0)
 
 
 def _skinny_ok(x, w) -> bool:
