@@ -51,6 +51,24 @@ def test_rmsnorm(H, out_dtype):
     close(out, want[[6, 0, 6]], 1e-6 if out_dtype == torch.float32 else 4e-3, "rmsnorm rows")
 
 
+@pytest.mark.parametrize("H,out_dtype", [(72, torch.float32), (1000, torch.bfloat16), (1536, torch.bfloat16),
+                                         (3584, torch.bfloat16), (5120, torch.float32), (8192, torch.bfloat16),
+                                         (8200, torch.bfloat16), (70, torch.float32)])
+def test_rmsnorm_many_rows(H, out_dtype):
+    """A prompt's rows go through the variant that holds a row in registers (widths up to 8192 in steps of
+    four); wider or odd rows fall to the general kernel.  Both give the plain result."""
+    from tq_kv_b200 import kernels
+    x, w = rnd(200, H, scale=3.0), rnd(H) + 1.0
+    x[17] *= 40.0                                            # rows of very different size
+    out = torch.empty(200, H, dtype=out_dtype, device=DEV)
+    kernels.rmsnorm(x, w, 1e-6, out)
+    want = pm.rms_norm(x.cpu(), w.cpu(), 1e-6)
+    close(out, want, 2e-6 if out_dtype == torch.float32 else 4e-3, "rmsnorm many rows")
+    rows = torch.arange(199, -1, -1, dtype=torch.int32, device=DEV)
+    kernels.rmsnorm(x, w, 1e-6, out, rows)
+    close(out, want.flip(0), 2e-6 if out_dtype == torch.float32 else 4e-3, "rmsnorm many rows, gathered")
+
+
 def test_swiglu_and_add_into():
     from tq_kv_b200 import kernels
     gu = rnd(5, 2 * 203, scale=2.0)

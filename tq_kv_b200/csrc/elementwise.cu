@@ -79,9 +79,63 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>((xr[i] / rms) * w[i]);
 }
 
+// Many rows (a prompt): a row is read once, held in registers between the sum of squares and the scaling
+// (VPT 16-byte loads per thread, all in flight together), by a block small enough that a whole wave of rows
+// is resident.  Same arithmetic as above.
+template <typename TO, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_cached_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                      const int* __restrict__ rows, int H, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x, h4 = H >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    TO* o = out + (size_t)r * H;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * THREADS;
+        v[i] = idx < h4 ? x4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rms = sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * THREADS;
+        if (idx < h4) {
+            const float4 g = w4[idx];
+            store2_f32<TO>(o + 4 * idx, (v[i].x / rms) * g.x, (v[i].y / rms) * g.y);
+            store2_f32<TO>(o + 4 * idx + 2, (v[i].z / rms) * g.z, (v[i].w / rms) * g.w);
+        }
+    }
+}
+
+template <typename TO>
+static int launch_rmsnorm_cached(const float* x, const float* w, TO* out, const int* rows, int n_rows, int H, float eps,
+                                 cudaStream_t stream) {
+    const int h4 = H >> 2;
+#define TQ_RN(T, V) rmsnorm_cached_kernel<TO, T, V><<<n_rows, T, 0, stream>>>(x, w, out, rows, H, eps)
+    if (h4 <= 128 * 2) TQ_RN(128, 2);
+    else if (h4 <= 128 * 4) TQ_RN(128, 4);
+    else if (h4 <= 128 * 8) TQ_RN(128, 8);
+    else TQ_RN(256, 8);
+#undef TQ_RN
+    return tq_launch_status();
+}
+
 TQ_API int tq_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int n_rows, int H,
                       float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (n_rows >= 128 && (H & 3) == 0 && H <= 256 * 8 * 4 && (out_dtype == TQ_F32 || out_dtype == TQ_BF16)) {
+        if (out_dtype == TQ_F32) return launch_rmsnorm_cached<float>(x, w, (float*)out, rows, n_rows, H, eps, stream);
+        return launch_rmsnorm_cached<bf16>(x, w, (bf16*)out, rows, n_rows, H, eps, stream);
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (out_dtype == TQ_F32)
         return tq_launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, w, (float*)out, rows,
