@@ -167,9 +167,11 @@ def test_skinny_gemm(M, N, K):
     close(out, wide[:, 32:32 + K].double() @ w.double().T, 1e-5 * math.sqrt(K / 64), "skinny strided")
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (1, 8, 8), (2048, 512, 3584), (257, 1000, 1096)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (1, 8, 8), (2048, 512, 3584), (257, 1000, 1096),
+                                   (512, 4608, 3584), (100, 3584, 2048)])
 def test_gemm_tc(M, N, K):
-    """The TMA + tcgen05 product: whole tiles, ragged edges in M, N and K, a long K."""
+    """The TMA + tcgen05 product: whole tiles, ragged edges in M, N and K, a long K; tiles fewer than the SMs,
+    which the float32 products cut along K (the plain store then clears C first and sums the shares)."""
     from tq_kv_b200 import kernels
     x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1), rnd(N, seed=2)
     want = x.double() @ w.double().T

@@ -373,6 +373,34 @@ static int make_map_c(CUtensorMap* map, const void* base, bool f32, uint64_t row
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
+// Into how many shares of K the tiles of the last, incomplete round are cut: rem * parts pieces of 1 / parts of
+// a tile each take ceil(rem * parts / sms) / parts tile times, plus a little for each share's epilogue.
+// *gain (optional): that time over the uncut round's.
+static int tc_last_round_parts(int n_tiles, int sms, int K, double* gain) {
+    const int rem = n_tiles % sms, k_all = (K + TC_BK - 1) / TC_BK;
+    int parts = 1;
+    double best = 1.0;
+    if (rem > 0) {
+        for (int p = 2; p <= 8 && k_all / p >= 8; ++p) {
+            const double t = (double)((rem * p + sms - 1) / sms) / p + 0.02 * p;
+            if (t < best - 1e-9) { best = t; parts = p; }
+        }
+    }
+    if (gain) *gain = best;
+    return parts;
+}
+
+static int tc_sm_count() {
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 1;
+    }
+    return sm_count;
+}
+
 template <int EPI, typename TO>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const float* bias, int M, int N,
                      int K, int b_rows_second, int* status, cudaStream_t stream) {
@@ -385,27 +413,15 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     }
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
     const int n_tiles = ((N + OUT_COLS - 1) / OUT_COLS) * ((M + TC_BM - 1) / TC_BM);
-    static int sm_count = 0;
-    if (!sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 1;
-    }
-    const int grid = n_tiles < sm_count ? n_tiles : sm_count;
-    // The tiles of an incomplete last round are cut along K into `parts` shares (residual epilogue only: the
-    // shares add up in C), with the number of shares that lets the round end soonest: rem * parts pieces of
-    // 1 / parts of a tile each take ceil(rem * parts / grid) / parts tile times.
+    const int sm_count = tc_sm_count();
+    // The tiles of an incomplete last round (all tiles, if they are fewer than the SMs) are cut along K into
+    // `parts` shares (residual epilogue only: the shares add up in C), with the number of shares that lets
+    // the round end soonest.
     int n_whole = n_tiles, parts = 1;
-    const int rem = n_tiles % grid, k_all = (K + TC_BK - 1) / TC_BK;
-    if (EPI == EPI_ACCUM && n_tiles > grid && rem > 0) {
-        double best = 1.0;
-        for (int p = 2; p <= 8 && k_all / p >= 8; ++p) {
-            const double t = (double)((rem * p + grid - 1) / grid) / p + 0.02 * p;   // a little for each share's epilogue
-            if (t < best - 1e-9) { best = t; parts = p; }
-        }
-        if (parts > 1) n_whole = n_tiles - rem;
-    }
+    if (EPI == EPI_ACCUM) parts = tc_last_round_parts(n_tiles, sm_count, K, nullptr);
+    if (parts > 1) n_whole = n_tiles - n_tiles % sm_count;
+    const int n_items = n_whole + (n_tiles - n_whole) * parts;
+    const int grid = n_items < sm_count ? n_items : sm_count;
     gemm_tc_kernel<EPI, TO><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(ma, mb, mc, bias, M, N, K, b_rows_second,
                                                                         n_whole, parts, status);
     return tq_launch_status();
@@ -438,7 +454,20 @@ TQ_API int tq_gemm_tc(const void* A, const void* B, const float* bias, void* C, 
     st = make_map_c(&mc, C, c_dtype == TQ_F32, (uint64_t)M, (uint64_t)N, (uint64_t)ldc);
     if (st) return st;
 #define TQ_TC(E, T) return launch_tc<E, T>(ma, mb, mc, bias, M, N, K, N, status, stream)
-    if (epilogue == EPI_STORE && c_dtype == TQ_F32) TQ_TC(EPI_STORE, float);
+    if (epilogue == EPI_STORE && c_dtype == TQ_F32) {
+        // A float32 result whose tiles fill the last round badly (few rows: 72 tiles on 148 SMs) is cleared and
+        // then summed from shares of K like the residual product; worth it when the last round is most of the
+        // work and the shares cut it by a third or more.
+        const int n_tiles = ((N + TC_BN - 1) / TC_BN) * ((M + TC_BM - 1) / TC_BM);
+        double gain = 1.0;
+        const int sms = tc_sm_count();
+        if (n_tiles < 2 * sms && tc_last_round_parts(n_tiles, sms, K, &gain) > 1 && gain <= 0.67) {
+            cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream);
+            if (e != cudaSuccess) return (int)e;
+            TQ_TC(EPI_ACCUM, float);
+        }
+        TQ_TC(EPI_STORE, float);
+    }
     if (epilogue == EPI_STORE && c_dtype == TQ_BF16) TQ_TC(EPI_STORE, bf16);
     if (epilogue == EPI_ACCUM) TQ_TC(EPI_ACCUM, float);
     if (epilogue == EPI_SWIGLU && c_dtype == TQ_F32) TQ_TC(EPI_SWIGLU, float);
