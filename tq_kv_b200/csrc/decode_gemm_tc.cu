@@ -15,6 +15,13 @@
 // rank order (no atomics: the result does not depend on scheduling).  Epilogues as in skinny_gemm.cu: bias, SwiGLU
 // gating, adding into the float32 residual stream, float32 or bfloat16 out.
 //
+// Float32 results without gating have a second way to split K (REDUCE): the
+// shares are independent blocks, as many as fill the GPU twice, and each hands
+// its partial tile to TMA as a reduce-add, which sums in the L2
+// (cp.reduce.async.bulk.tensor); a result that is not added to the residual
+// stream is cleared first.  No cluster, no exchange through shared memory;
+// the order of the float additions of one output is then not fixed.
+//
 // All waits on mbarriers are bounded (see gemm_tc.cu): a wait that runs out
 // raises a bit in *status, the block still frees its TMEM and returns.
 #include <cooperative_groups.h>
@@ -67,11 +74,11 @@ __device__ __forceinline__ void dg_ld32(uint32_t taddr, float* v) {
 
 // MP: padded batch (32 or 64) = columns of the accumulator.
 // DG_STAGES: 4 (96 KB per block: two blocks fit an SM, one's epilogue runs under the other's loads) or 8.
-template <int MP, bool SWIGLU, typename TO, int DG_STAGES>
+template <int MP, bool SWIGLU, typename TO, int DG_STAGES, bool REDUCE>
 __global__ void __launch_bounds__(DG_THREADS, DG_STAGES == 4 ? 2 : 1)
 decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                      const float* __restrict__ bias, TO* __restrict__ Y, int M, int N, int K, int ldy, int accumulate,
-                      int* __restrict__ status) {
+                      const __grid_constant__ CUtensorMap map_y, const float* __restrict__ bias, TO* __restrict__ Y,
+                      int M, int N, int K, int ldy, int accumulate, int k_splits, int* __restrict__ status) {
     constexpr int X_BYTES = MP * DG_BK * 2;
     constexpr int STAGE_BYTES = DG_W_BYTES + X_BYTES;
     constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
@@ -88,8 +95,9 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     volatile uint32_t* failed = tmem_slot + 1;
 
     cg::cluster_group cluster = cg::this_cluster();
-    const int n_ranks = (int)cluster.num_blocks();
-    const int rank = (int)cluster.block_rank();
+    // shares of K: the blocks of a cluster, or (REDUCE) k_splits independent blocks in a row of the grid
+    const int n_ranks = REDUCE ? k_splits : (int)cluster.num_blocks();
+    const int rank = REDUCE ? (int)(blockIdx.x % k_splits) : (int)cluster.block_rank();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = (blockIdx.x / n_ranks) * OUT_COLS;
     const int k_total = (K + DG_BK - 1) / DG_BK;
@@ -163,6 +171,48 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                      ::"r"(dg_smem(acc_full)) : "memory");
     }
     __syncwarp();
+
+    if (REDUCE) {
+        // ---- the partial tile -> shared memory as [batch row][32 outputs] per warp -> TMA reduce-add into Y.
+        // A thread holds one output (weight row) for all batch rows; for each batch row the warp's 32 values
+        // are neighbours in memory.  TMA clips batch rows >= M and outputs >= N. ----
+        if (warp >= 2) {
+            const bool good = k_iters == 0 || dg_wait(dg_smem(acc_full), 0, true);
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int quarter = warp & 3;
+            const int col = n0 + quarter * 32 + lane;
+            float* piece = reinterpret_cast<float*>(tiles) + quarter * MP * 32;
+            if (good && k_iters > 0 && n0 + quarter * 32 < N) {
+                const float bv = (bias != nullptr && rank == 0 && col < N) ? bias[col] : 0.f;
+#pragma unroll
+                for (int c = 0; c < MP; c += 32) {
+                    float v[32];
+                    dg_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) piece[(c + j) * 32 + lane] = v[j] + bv;
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile(
+                        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];\n"
+                        ::"l"(&map_y), "r"(n0 + quarter * 32), "r"(0), "r"(dg_smem(piece)) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+                }
+            }
+            if (!good) *failed = 1;
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncthreads();
+        if (threadIdx.x == 0 && *failed && status) atomicOr(status, 2);
+        if (warp == 1) {
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)MP)
+                         : "memory");
+        }
+        return;
+    }
 
     // ---- the accumulator -> shared memory (all stages are free once it is complete) ----
     bool good = true;
@@ -248,9 +298,45 @@ static int dg_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
-static int g_force_ranks = 0;       // tuning aids: fixed cluster size / stage count instead of the heuristics
+static int g_force_ranks = 0;       // tuning aids: fixed number of K shares (negative: as a cluster) / stage count
 static int g_force_stages = 0;
 TQ_API void tq_decode_gemm_tc_force(int ranks, int stages) { g_force_ranks = ranks; g_force_stages = stages; }
+
+// The REDUCE form: tiles x splits independent blocks, partial tiles summed into Y by TMA.
+template <int MP>
+static int dg_launch_reduce(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, float* Y, int M, int N,
+                            int K, int ldy, int accumulate, int* status, int splits, cudaStream_t stream) {
+    constexpr int STAGES = 4;
+    constexpr int STAGE_BYTES = DG_W_BYTES + MP * DG_BK * 2;
+    constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(4 * MP * 32 * 4 <= STAGES * STAGE_BYTES, "the partial tile must fit in the stages");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_gemm_tc_kernel<MP, false, float, STAGES, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap my;
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+        const cuuint64_t strides[1] = {(cuuint64_t)ldy * 4};
+        const cuuint32_t box[2] = {32, (cuuint32_t)MP};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = cuTensorMapEncodeTiled(&my, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, Y, dims, strides, box, estr,
+                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    }
+    if (!accumulate) {
+        cudaError_t e = cudaMemset2DAsync(Y, (size_t)ldy * 4, 0, (size_t)N * 4, (size_t)M, stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int tiles = (N + DG_ROWS - 1) / DG_ROWS;
+    decode_gemm_tc_kernel<MP, false, float, STAGES, true><<<tiles * splits, DG_THREADS, SMEM, stream>>>(
+        mw, mx, my, bias, Y, M, N, K, ldy, 1, splits, status);
+    return tq_launch_status();
+}
 
 template <int MP, bool SWIGLU, typename TO, int DG_STAGES>
 static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* Y, int M, int N, int K,
@@ -260,7 +346,7 @@ static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float
     static_assert(DG_ROWS * (MP + 1) * 4 <= DG_STAGES * STAGE_BYTES, "partial sums must fit in the stages");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -279,8 +365,9 @@ static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES>, mw, mx, bias, (TO*)Y, M,
-                                       N, K, ldy, accumulate, status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false>, mw, mx,
+                                       mw /* no map of Y in this form */, bias, (TO*)Y, M, N, K, ldy, accumulate, 1,
+                                       status);
     if (e != cudaSuccess) return (int)e;
     return tq_launch_status();
 }
@@ -291,12 +378,31 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
     constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
     const int tiles = (N + OUT_COLS - 1) / OUT_COLS;
     const int k_total = (K + DG_BK - 1) / DG_BK;
+    // Float32 results without gating whose tiles do not fill the GPU's block slots (two per SM): independent
+    // shares of K of at least 8 steps, as many as still run in one wave, summed by TMA.  Y must be fit for TMA
+    // (16-byte aligned base and row stride).
+    static int slots = 0;
+    if (!slots) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        slots = 2 * (sms > 0 ? sms : 1);
+    }
+    if (!SWIGLU && sizeof(TO) == 4 && g_force_ranks >= 0 && k_total >= 16 &&
+        (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (ldy & 3) == 0) {
+        int splits = slots / tiles;
+        if (splits > k_total / 8) splits = k_total / 8;
+        if (g_force_ranks > 0) splits = g_force_ranks;
+        if (splits > 1)
+            return dg_launch_reduce<MP>(mw, mx, bias, (float*)Y, M, N, K, ldy, accumulate, status, splits, stream);
+    }
     // split K while the grid is small and the shares stay long.  Measured best on the 7B shapes: up to 4
     // blocks and about 64 blocks in all for batches over 16 rows, up to 8 and a full GPU for smaller ones.
     const int max_ranks = M > 16 ? 4 : 8, want_blocks = M > 16 ? 64 : 148;
     int ranks = 1;
     while (ranks < max_ranks && tiles * ranks < want_blocks && k_total / (ranks * 2) >= 4) ranks *= 2;
     if (g_force_ranks > 0) ranks = g_force_ranks;
+    if (g_force_ranks < 0) ranks = -g_force_ranks;                 // negative: the cluster form with that many blocks
     int stages = 4;
     if (g_force_stages > 0) stages = g_force_stages;
     if (stages == 8) return dg_launch_s<MP, SWIGLU, TO, 8>(mw, mx, bias, Y, M, N, K, ldy, accumulate, status, ranks, stream);
