@@ -250,7 +250,7 @@ def main() -> int:
                    "intermediate_size": cfg["intermediate_size"], "vocab_size": V, "global_batch": args.batch,
                    "seq_len": args.context, "prompt_len": args.prompt, "decode_ctx_start": start_ctx + W,
                    "parallelism": "single GPU", "weights": "random N(0,0.02) bf16",
-                   "l2": "step reads >14 GB of weights, far more than the 126 MB L2",
+                   "l2": f"a step reads {nums['weight_bytes'] / 1e9:.1f} GB of weights, more than the 126 MB L2",
                    "peaks": pk_src},
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
