@@ -125,11 +125,13 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    // Programmatic dependent launch (common.cuh): the weights do not depend on the kernel before, so the first
+    // stages' W tiles are requested before waiting for it; X, bias and Y are touched only after pdl_wait().
+    if (!(warp == 0 && lane == 0)) { pdl_wait(); pdl_launch(); }
     if (warp == 0 && lane == 0) {
         // ---- producer ----
-        for (int i = 0; i < k_iters; ++i) {
+        auto load_w = [&](int i) {
             const int s = i % DG_STAGES;
-            if (!dg_wait(dg_smem(&empty[s]), ((i / DG_STAGES) & 1) ^ 1)) { *failed = 1; break; }
             const uint32_t fb = dg_smem(&full[s]);
             const uint32_t w_dst = dg_smem(tiles + s * STAGE_BYTES);
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(fb), "r"((uint32_t)STAGE_BYTES)
@@ -141,7 +143,21 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             } else {
                 dg_tma(w_dst, &map_w, kc, n0, fb);
             }
-            dg_tma(w_dst + DG_W_BYTES, &map_x, kc, 0, fb);
+        };
+        auto load_x = [&](int i) {
+            const int s = i % DG_STAGES;
+            dg_tma(dg_smem(tiles + s * STAGE_BYTES) + DG_W_BYTES, &map_x, (k_lo + i) * DG_BK, 0, dg_smem(&full[s]));
+        };
+        const int ahead = k_iters < DG_STAGES ? k_iters : DG_STAGES;     // the stages are empty at the start
+        for (int i = 0; i < ahead; ++i) load_w(i);
+        pdl_wait();
+        pdl_launch();
+        for (int i = 0; i < ahead; ++i) load_x(i);
+        for (int i = ahead; i < k_iters; ++i) {
+            const int s = i % DG_STAGES;
+            if (!dg_wait(dg_smem(&empty[s]), ((i / DG_STAGES) & 1) ^ 1)) { *failed = 1; break; }
+            load_w(i);
+            load_x(i);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: D[128 x MP] (+)= W_tile[128 x 64] · X_tile[MP x 64]^T ----
@@ -333,9 +349,8 @@ static int dg_launch_reduce(const CUtensorMap& mw, const CUtensorMap& mx, const 
         if (e != cudaSuccess) return (int)e;
     }
     const int tiles = (N + DG_ROWS - 1) / DG_ROWS;
-    decode_gemm_tc_kernel<MP, false, float, STAGES, true><<<tiles * splits, DG_THREADS, SMEM, stream>>>(
-        mw, mx, my, bias, Y, M, N, K, ldy, 1, splits, status);
-    return tq_launch_status();
+    return tq_launch_pdl(decode_gemm_tc_kernel<MP, false, float, STAGES, true>, dim3(tiles * splits), dim3(DG_THREADS),
+                         SMEM, stream, mw, mx, my, bias, Y, M, N, K, ldy, 1, splits, status);
 }
 
 template <int MP, bool SWIGLU, typename TO, int DG_STAGES>
@@ -358,13 +373,15 @@ static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float
     cfg.blockDim = dim3(DG_THREADS, 1, 1);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = ranks;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = tq_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false>, mw, mx,
                                        mw /* no map of Y in this form */, bias, (TO*)Y, M, N, K, ldy, accumulate, 1,
                                        status);
