@@ -248,7 +248,7 @@ def test_a_wait_that_ran_out_is_reported_by_the_host_check():
     kernels.gemm_tc(x, w, out)
     kernels.check_tc_status()                                        # a healthy launch passes
     kernels.gemm_tc(x, w, out)
-    kernels.gemm._status_for(x.device).fill_(2)
+    kernels._lib.tc_status_word(x.device).fill_(2)
     with pytest.raises(kernels.KernelError, match="wait ran out"):
         kernels.check_tc_status()
     kernels.gemm_tc(x, w, out)

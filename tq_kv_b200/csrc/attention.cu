@@ -211,10 +211,10 @@ TQ_API int tq_attention_merge(const float* part_acc, const float* part_ml, void*
     if (n_splits < 1 || !part_acc || !part_ml) return (int)cudaErrorInvalidValue;
     const dim3 mgrid(n_tokens, nh);
     if (dtype == TQ_F32)
-        return tq_launch_pdl(attention_merge_kernel<float>, mgrid, dim3(128), 0, stream, part_acc, part_ml,
+        return tq_launch_pdl(TQ_PDL_MERGE, attention_merge_kernel<float>, mgrid, dim3(128), 0, stream, part_acc, part_ml,
                              (float*)out, nh, hd, n_splits);
     if (dtype == TQ_BF16)
-        return tq_launch_pdl(attention_merge_kernel<bf16>, mgrid, dim3(128), 0, stream, part_acc, part_ml,
+        return tq_launch_pdl(TQ_PDL_MERGE, attention_merge_kernel<bf16>, mgrid, dim3(128), 0, stream, part_acc, part_ml,
                              (bf16*)out, nh, hd, n_splits);
     return (int)cudaErrorInvalidValue;
 }

@@ -112,28 +112,44 @@ static inline int tq_launch_status() { return (int)cudaGetLastError(); }
 // Kernels of a decode step are short and run back to back.  Launched with
 // this attribute, a kernel may start while its predecessor in the stream is
 // still draining: it does whatever does not depend on the predecessor (index
-// arithmetic, prefetching weights), then pdl_wait() blocks until the
-// predecessor has completed and its writes are visible.  Every kernel
+// arithmetic, requesting its first weight tiles), then pdl_wait() blocks until
+// the predecessor has completed and its writes are visible.  Every kernel
 // launched this way calls pdl_wait() before it reads or writes anything a
 // predecessor may touch, and pdl_launch() right after, which lets its own
-// successor start early in turn.  Measured on the 7B decode step the overlap
-// gained 3 % at batch 1 and lost 12 % at batch 8, so it is off unless TQ_PDL=1
-// is set; without the launch attribute both instructions do nothing.
+// successor start early in turn.  Without the launch attribute both
+// instructions do nothing.
+//
+// Measured on decode steps by kernel family: every family gains a little or
+// nothing alone, the attention merge loses, and all but the merge together
+// gain 2 to 3 % on the 7B shape and 3 to 14 % on the 0.5B shape, whose step is
+// mostly launch latency.  So that is the default.  TQ_PDL=0 switches it off,
+// TQ_PDL=1 on for every family, a larger number is a mask of families:
+// 2 element-wise, 4 skinny_gemm, 8 decode_gemm_tc, 16 flash_decode,
+// 32 attention merge, 64 sampling.  Every launch names its family.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-static inline bool tq_pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
+#define TQ_PDL_ELEMENTWISE 2
+#define TQ_PDL_SKINNY 4
+#define TQ_PDL_DECODE_GEMM 8
+#define TQ_PDL_FLASH_DECODE 16
+#define TQ_PDL_MERGE 32
+#define TQ_PDL_SAMPLING 64
+#define TQ_PDL_DEFAULT (TQ_PDL_ELEMENTWISE | TQ_PDL_SKINNY | TQ_PDL_DECODE_GEMM | TQ_PDL_FLASH_DECODE | TQ_PDL_SAMPLING)
+static inline bool tq_pdl_enabled(int family) {
+    static int mask = -1;
+    if (mask < 0) {
         const char* e = getenv("TQ_PDL");
-        on = (e && e[0] == '1') ? 1 : 0;
+        mask = e ? atoi(e) : TQ_PDL_DEFAULT;
+        if (mask == 1) mask = 0x7fffffff;
+        if (mask < 0) mask = 0;
     }
-    return on == 1;
+    return (mask & family) != 0;
 }
 
 template <typename... KArgs, typename... Args>
-static inline int tq_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                Args... args) {
+static inline int tq_launch_pdl(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -141,7 +157,7 @@ static inline int tq_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = tq_pdl_enabled() ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = tq_pdl_enabled(family) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);

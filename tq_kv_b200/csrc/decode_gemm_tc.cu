@@ -349,7 +349,7 @@ static int dg_launch_reduce(const CUtensorMap& mw, const CUtensorMap& mx, const 
         if (e != cudaSuccess) return (int)e;
     }
     const int tiles = (N + DG_ROWS - 1) / DG_ROWS;
-    return tq_launch_pdl(decode_gemm_tc_kernel<MP, false, float, STAGES, true>, dim3(tiles * splits), dim3(DG_THREADS),
+    return tq_launch_pdl(TQ_PDL_DECODE_GEMM, decode_gemm_tc_kernel<MP, false, float, STAGES, true>, dim3(tiles * splits), dim3(DG_THREADS),
                          SMEM, stream, mw, mx, my, bias, Y, M, N, K, ldy, 1, splits, status);
 }
 
@@ -379,7 +379,7 @@ static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = tq_pdl_enabled() ? 1 : 0;
+    attr[1].val.programmaticStreamSerializationAllowed = tq_pdl_enabled(TQ_PDL_DECODE_GEMM) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false>, mw, mx,

@@ -30,10 +30,10 @@ TQ_API int tq_embed(const int* tokens, const void* table, int table_dtype, float
     if (n_tokens <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == TQ_F32)
-        return tq_launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
                              (const float*)table, out, H, V, status);
     if (table_dtype == TQ_BF16)
-        return tq_launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
                              (const bf16*)table, out, H, V, status);
     return (int)cudaErrorInvalidValue;
 }
@@ -138,10 +138,10 @@ TQ_API int tq_rmsnorm(const float* x, const float* w, void* out, int out_dtype, 
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (out_dtype == TQ_F32)
-        return tq_launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, w, (float*)out, rows,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, w, (float*)out, rows,
                              H, eps);
     if (out_dtype == TQ_BF16)
-        return tq_launch_pdl(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, w, (bf16*)out, rows, H,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, w, (bf16*)out, rows, H,
                              eps);
     return (int)cudaErrorInvalidValue;
 }
@@ -327,14 +327,14 @@ TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, c
     // many tokens: one block per token with 16-byte accesses; few tokens (decoding): one block per (token, head)
     if (n_tokens >= 128 && in_dtype == TQ_F32 && cache_dtype == TQ_BF16 && rot == hd && (hd & 7) == 0 &&
         (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0))
-        return tq_launch_pdl(qkv_rope_cache_vec_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)qkv,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, qkv_rope_cache_vec_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)qkv,
                              bias, cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width,
                              ring_pages, page_tokens, (bf16*)q_out, (bf16*)k_out, (bf16*)v_out, (bf16*)k_pages,
                              (bf16*)v_pages, nh, nkv, hd);
     const int threads = hd >= 128 ? 64 : 32;
     const dim3 grid(n_tokens, nh + 2 * nkv);
 #define TQ_LAUNCH(TI, TC)                                                                                       \
-    return tq_launch_pdl(qkv_rope_cache_kernel<TI, TC>, grid, dim3(threads), 0, stream, (const TI*)qkv, bias,  \
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, qkv_rope_cache_kernel<TI, TC>, grid, dim3(threads), 0, stream, (const TI*)qkv, bias,  \
                          cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width, ring_pages,   \
                          page_tokens, (TC*)q_out, (TC*)k_out, (TC*)v_out, (TC*)k_pages, (TC*)v_pages, nh, nkv, \
                          hd, rot)

@@ -277,7 +277,7 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
         configured = true;
     }
     const dim3 grid(n_tokens, nkv, n_splits);
-    return tq_launch_pdl(flash_decode_kernel<HD, FD_CHUNK>, grid, dim3(FD_WARPS * 32), smem, stream, q, kp, vp, table,
+    return tq_launch_pdl(TQ_PDL_FLASH_DECODE, flash_decode_kernel<HD, FD_CHUNK>, grid, dim3(FD_WARPS * 32), smem, stream, q, kp, vp, table,
                          table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out, part_acc,
                          part_ml, nh, nkv, n_splits);
 }

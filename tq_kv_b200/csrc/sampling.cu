@@ -481,10 +481,10 @@ TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float tempe
     if (temperature > 0.f && !uniforms) return (int)cudaErrorInvalidValue;
     if (counts && !(penalty > 0.f)) return (int)cudaErrorInvalidValue;
     if (temperature <= 0.f && scratch && n_rows <= 65535) {
-        int st = tq_launch_pdl(argmax_parts_kernel, dim3(n_rows, ARGMAX_PARTS), dim3(256), 0, stream, logits, ld, V,
+        int st = tq_launch_pdl(TQ_PDL_SAMPLING, argmax_parts_kernel, dim3(n_rows, ARGMAX_PARTS), dim3(256), 0, stream, logits, ld, V,
                                (const int*)counts, penalty, (ArgMax*)scratch);
         if (st) return st;
-        return tq_launch_pdl(argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, (const ArgMax*)scratch, counts, V,
+        return tq_launch_pdl(TQ_PDL_SAMPLING, argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, (const ArgMax*)scratch, counts, V,
                              out);
     }
     if (temperature > 0.f && scratch && top_k > 0 && top_k <= TOPK_MAX && n_rows <= 65535 &&
@@ -492,13 +492,13 @@ TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float tempe
         float* cand_val = (float*)scratch;
         int* cand_idx = (int*)(cand_val + (size_t)n_rows * TOPK_PARTS * TOPK_CAP);
         int* cand_cnt = cand_idx + (size_t)n_rows * TOPK_PARTS * TOPK_CAP;
-        int st = tq_launch_pdl(topk_parts_kernel, dim3(n_rows, TOPK_PARTS), dim3(256), 0, stream, logits, ld, V,
+        int st = tq_launch_pdl(TQ_PDL_SAMPLING, topk_parts_kernel, dim3(n_rows, TOPK_PARTS), dim3(256), 0, stream, logits, ld, V,
                                (const int*)counts, penalty, top_k, cand_val, cand_idx, cand_cnt);
         if (st) return st;
-        return tq_launch_pdl(topk_final_kernel, dim3(n_rows), dim3(256), 0, stream, (const float*)cand_val,
+        return tq_launch_pdl(TQ_PDL_SAMPLING, topk_final_kernel, dim3(n_rows), dim3(256), 0, stream, (const float*)cand_val,
                              (const int*)cand_idx, (const int*)cand_cnt, V, temperature, top_k, top_p, uniforms,
                              counts, out);
     }
-    return tq_launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
+    return tq_launch_pdl(TQ_PDL_SAMPLING, sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
                          top_k, top_p, uniforms, counts, penalty, out);
 }

@@ -207,7 +207,7 @@ static int launch_skinny(const bf16* X, const bf16* W, const float* bias, void* 
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;      // see pdl_wait() in the kernel
-    attr[1].val.programmaticStreamSerializationAllowed = tq_pdl_enabled() ? 1 : 0;
+    attr[1].val.programmaticStreamSerializationAllowed = tq_pdl_enabled(TQ_PDL_SKINNY) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TW, SWIGLU, TO>, X, W, bias, (TO*)Y, M, N, K, ldx,

@@ -53,6 +53,35 @@ def check(status: int, what: str, n_kernels: int = 1) -> None:
     launches[0] += n_kernels
 
 
+# ---- the status word of the tcgen05 kernels ---------------------------------------
+# Their mbarrier waits are bounded; a wait that runs out raises a bit in this device word instead of hanging
+# (2: a matrix product, 4: the prompt attention, 8: its shared memory was not aligned).
+_tc_status: dict = {}               # device -> int32[1]
+_tc_launched = [0]
+
+
+def tc_status_word(device) -> torch.Tensor:
+    """The device word a tcgen05 kernel launched now reports into; notes that one was launched."""
+    t = _tc_status.get(device)
+    if t is None:
+        t = _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    _tc_launched[0] += 1
+    return t
+
+
+def check_tc_status() -> None:
+    """Raises if a tcgen05 kernel launched since the last check gave up on a
+    pipeline wait (its output is then invalid).  Synchronises with the device."""
+    if not _tc_launched[0]:
+        return
+    _tc_launched[0] = 0
+    for dev, t in _tc_status.items():
+        v = int(t.item())
+        if v:
+            t.zero_()
+            raise KernelError(f"a tcgen05 kernel on {dev}: a pipeline wait ran out (status {v}); results are invalid")
+
+
 _SIGNATURES = {
     "tq_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "tq_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],

@@ -6,7 +6,7 @@ from typing import Optional
 
 import torch
 
-from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream
+from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream, tc_status_word
 
 MAX_HEAD_DIM = 256
 NOT_SUPPORTED = 801     # cudaErrorNotSupported: a specialised kernel declines the shape
@@ -80,15 +80,13 @@ def attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: i
     n_seqs = cu_seqlens.shape[0] - 1
     if q.dtype == torch.bfloat16 and use_flash and USE_TC_ATTENTION and T > n_seqs:
         # prompts on the tcgen05 tensor cores (128-query tiles, S and P·V in tensor memory)
-        from .gemm import _status_for, _tc_launched
         st = core().tq_flash_prefill_tc(
             ptr(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages),
             0 if k_pages is None else k_pages.shape[0], ptr(block_table), table_width, ring_pages, page_tokens,
             ptr(cu_seqlens), ptr(start_pos), n_seqs, T, int(window or 0), float(scale), ptr(out), n_heads,
-            n_kv_heads, head_dim, ptr(_status_for(q.device)), stream())
+            n_kv_heads, head_dim, ptr(tc_status_word(q.device)), stream())
         if st != NOT_SUPPORTED:
             check(st, "flash_prefill_tc")
-            _tc_launched[0] += 1
             return out
     if q.dtype == torch.bfloat16 and use_flash and T > n_seqs:
         # prompts (some sequence brings several tokens): the tensor-core kernel with 64-query tiles

@@ -23,7 +23,7 @@ from typing import Optional
 import torch
 
 from . import elementwise
-from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream
+from ._lib import KernelError, check, check_tc_status, core, dtype_code, need_contiguous, ptr, stream, tc_status_word
 
 ROW_KERNEL_MAX_ROWS = 16
 SKINNY_MAX_ROWS = 64
@@ -43,15 +43,6 @@ def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
 # ---- tcgen05 + TMA product for many rows (csrc/gemm_tc.cu) -----------------------
 USE_TCGEN05 = True                  # False: the library product (cuBLAS) takes the many-row bfloat16 case
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
-_tc_status: dict = {}               # device -> int32[1]; bit 1 = a pipeline wait of the kernel ran out
-_tc_launched = [0]
-
-
-def _status_for(device) -> torch.Tensor:
-    t = _tc_status.get(device)
-    if t is None:
-        t = _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
-    return t
 
 
 def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE):
@@ -61,8 +52,7 @@ def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE):
     M, K = x.shape
     N = out.shape[1]
     check(core().tq_gemm_tc(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0), w.stride(0),
-                            out.stride(0), epilogue, ptr(_status_for(x.device)), stream()), "gemm_tc")
-    _tc_launched[0] += 1
+                            out.stride(0), epilogue, ptr(tc_status_word(x.device)), stream()), "gemm_tc")
     return out
 
 
@@ -74,22 +64,8 @@ def decode_gemm_tc(x, w, out, bias=None, accumulate=False, swiglu=False):
     N = out.shape[1]
     check(core().tq_decode_gemm_tc(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0),
                                    w.stride(0), out.stride(0), int(accumulate), int(swiglu),
-                                   ptr(_status_for(x.device)), stream()), "decode_gemm_tc")
-    _tc_launched[0] += 1
+                                   ptr(tc_status_word(x.device)), stream()), "decode_gemm_tc")
     return out
-
-
-def check_tc_status() -> None:
-    """Raises if a tcgen05 product launched since the last check gave up on a
-    pipeline wait (its output is then invalid).  Synchronises with the device."""
-    if not _tc_launched[0]:
-        return
-    _tc_launched[0] = 0
-    for dev, t in _tc_status.items():
-        v = int(t.item())
-        if v:
-            t.zero_()
-            raise KernelError(f"gemm_tc on {dev}: a pipeline wait ran out (status {v}); results are invalid")
 
 
 def _tc_ok(x, w, out, swiglu) -> bool:
