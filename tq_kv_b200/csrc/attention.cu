@@ -148,21 +148,28 @@ template <typename TC>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        TC* __restrict__ out, int nh, int hd, int n_splits) {
     const size_t r0 = ((size_t)blockIdx.x * nh + blockIdx.y) * n_splits;
+    const int lane = threadIdx.x & 31;
     pdl_wait();
     pdl_launch();
+    // every warp finds the maximum and the sum for itself, its lanes striding over the splits
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[2 * (r0 + s)]);
+    for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, part_ml[2 * (r0 + s)]);
+    m = warp_max(m);
     float l = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
+    for (int s = lane; s < n_splits; s += 32) {
         const float ms = part_ml[2 * (r0 + s)];
         if (ms > -INFINITY) l += part_ml[2 * (r0 + s) + 1] * expf(ms - m);
     }
+    l = warp_sum(l);
     TC* o = out + ((size_t)blockIdx.x * nh + blockIdx.y) * hd;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float a = 0.f;
+        // the loads do not wait for one another: a split without keys is dropped after its load, not around it
+#pragma unroll 4
         for (int s = 0; s < n_splits; ++s) {
             const float ms = part_ml[2 * (r0 + s)];
-            if (ms > -INFINITY) a += part_acc[(r0 + s) * hd + d] * expf(ms - m);
+            const float v = part_acc[(r0 + s) * hd + d];
+            a += ms > -INFINITY ? v * expf(ms - m) : 0.f;
         }
         o[d] = from_f32<TC>(a / l);
     }

@@ -79,20 +79,28 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>((xr[i] / rms) * w[i]);
 }
 
-// Many rows (a prompt): a row is read once, held in registers between the sum of squares and the scaling
-// (VPT 16-byte loads per thread, all in flight together), by a block small enough that a whole wave of rows
-// is resident.  Same arithmetic as above.
+// Rows of up to 8,192 values in steps of four: a row is read once and held in registers between the sum of
+// squares and the scaling (VPT 16-byte loads per thread, all in flight together, the norm's weights with them).
+// A prompt's many rows get small blocks, so that a whole wave of rows is resident; the few rows of a decode
+// step get wide ones, so that a row is one round of loads.  Same arithmetic as above.
 template <typename TO, int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_cached_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
                       const int* __restrict__ rows, int H, float eps) {
     __shared__ float red[32];
     const int r = blockIdx.x, h4 = H >> 2;
-    const float4* x4 = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
     const float4* w4 = reinterpret_cast<const float4*>(w);
     TO* o = out + (size_t)r * H;
-    float4 v[VPT];
+    float4 v[VPT], g[VPT];
     float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {                        // the weights do not depend on the kernel before
+        const int idx = threadIdx.x + i * THREADS;
+        g[i] = idx < h4 ? w4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    pdl_launch();
+    const float4* x4 = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int idx = threadIdx.x + i * THREADS;
@@ -109,9 +117,8 @@ rmsnorm_cached_kernel(const float* __restrict__ x, const float* __restrict__ w, 
     for (int i = 0; i < VPT; ++i) {
         const int idx = threadIdx.x + i * THREADS;
         if (idx < h4) {
-            const float4 g = w4[idx];
-            store2_f32<TO>(o + 4 * idx, (v[i].x / rms) * g.x, (v[i].y / rms) * g.y);
-            store2_f32<TO>(o + 4 * idx + 2, (v[i].z / rms) * g.z, (v[i].w / rms) * g.w);
+            store2_f32<TO>(o + 4 * idx, (v[i].x / rms) * g[i].x, (v[i].y / rms) * g[i].y);
+            store2_f32<TO>(o + 4 * idx + 2, (v[i].z / rms) * g[i].z, (v[i].w / rms) * g[i].w);
         }
     }
 }
@@ -120,19 +127,26 @@ template <typename TO>
 static int launch_rmsnorm_cached(const float* x, const float* w, TO* out, const int* rows, int n_rows, int H, float eps,
                                  cudaStream_t stream) {
     const int h4 = H >> 2;
-#define TQ_RN(T, V) rmsnorm_cached_kernel<TO, T, V><<<n_rows, T, 0, stream>>>(x, w, out, rows, H, eps)
+#define TQ_RN(T, V)                                                                                                 \
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, rmsnorm_cached_kernel<TO, T, V>, dim3(n_rows), dim3(T), 0, stream, x, w, \
+                         out, rows, H, eps)
+    if (n_rows < 128) {                                    // a decode step: wide blocks
+        if (h4 <= 128) TQ_RN(128, 1);
+        if (h4 <= 512) TQ_RN(512, 1);
+        if (h4 <= 1024) TQ_RN(512, 2);
+        TQ_RN(512, 4);
+    }
     if (h4 <= 128 * 2) TQ_RN(128, 2);
-    else if (h4 <= 128 * 4) TQ_RN(128, 4);
-    else if (h4 <= 128 * 8) TQ_RN(128, 8);
-    else TQ_RN(256, 8);
+    if (h4 <= 128 * 4) TQ_RN(128, 4);
+    if (h4 <= 128 * 8) TQ_RN(128, 8);
+    TQ_RN(256, 8);
 #undef TQ_RN
-    return tq_launch_status();
 }
 
 TQ_API int tq_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int n_rows, int H,
                       float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (n_rows >= 128 && (H & 3) == 0 && H <= 256 * 8 * 4 && (out_dtype == TQ_F32 || out_dtype == TQ_BF16)) {
+    if ((H & 3) == 0 && H <= 256 * 8 * 4 && (out_dtype == TQ_F32 || out_dtype == TQ_BF16)) {
         if (out_dtype == TQ_F32) return launch_rmsnorm_cached<float>(x, w, (float*)out, rows, n_rows, H, eps, stream);
         return launch_rmsnorm_cached<bf16>(x, w, (bf16*)out, rows, n_rows, H, eps, stream);
     }
