@@ -184,9 +184,9 @@ __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* _
                                       TC* __restrict__ k_out, TC* __restrict__ v_out, TC* __restrict__ k_pages,
                                       TC* __restrict__ v_pages, int nh, int nkv, int hd, int rot) {
     // grid (token, head): heads 0..nh-1 are q, nh..nh+nkv-1 are k, the rest are v
+    // The step's positions and tables were copied in before its first kernel ran: only qkv depends on the
+    // kernel before, so the addressing is done before waiting for it.
     const int t = blockIdx.x, head = blockIdx.y;
-    pdl_wait();
-    pdl_launch();
     const int pos = tok_pos[t];
     const int b = tok_seq[t];
     const int half = rot >> 1;
@@ -214,6 +214,8 @@ __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* _
     TC* dst = is_q ? q_out + ((size_t)t * nh + head) * hd
                    : (is_k ? (k_out ? k_out + ((size_t)t * nkv + g) * hd : nullptr)
                            : (v_out ? v_out + ((size_t)t * nkv + g) * hd : nullptr));
+    pdl_wait();
+    pdl_launch();
     if (is_q || is_k) {
         const float* cs = cos_tab + (size_t)pos * half;
         const float* sn = sin_tab + (size_t)pos * half;

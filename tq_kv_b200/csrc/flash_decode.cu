@@ -61,8 +61,6 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tid4 = lane & 3;
     const int n_rep = nh / nkv;
-    pdl_wait();                                            // q and this step's keys come from the predecessors
-    pdl_launch();
     const int pos = tok_pos[t];
     const int b = tok_seq[t];
     const int lo_all = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -76,20 +74,6 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int n_chunks = hi > lo ? (hi - lo + FD_CHUNK - 1) / FD_CHUNK : 0;
     unsigned char* my = smem + warp * WARP_BYTES;
     const int* table = block_table + (size_t)b * table_width;
-
-    // Q fragments: rows = q heads of this group (rows >= n_rep are zero)
-    uint32_t qf[KS][4];
-    {
-        const bf16* q0 = q + ((size_t)t * nh + (size_t)g * n_rep) * HD;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            const int d = ks * 16 + 2 * tid4;
-            qf[ks][0] = gid < n_rep ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)gid * HD + d) : 0u;
-            qf[ks][1] = gid + 8 < n_rep ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(gid + 8) * HD + d) : 0u;
-            qf[ks][2] = gid < n_rep ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)gid * HD + d + 8) : 0u;
-            qf[ks][3] = gid + 8 < n_rep ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(gid + 8) * HD + d + 8) : 0u;
-        }
-    }
 
     // issue the copy of this warp's i-th chunk into stage i % FD_STAGES.  Lane l < FD_CHUNK looks up the row
     // of key l; then consecutive lanes copy consecutive 16-byte pieces of a row, so that every 32-byte
@@ -123,8 +107,36 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
 
     const int my_chunks = n_chunks > warp ? (n_chunks - warp + FD_WARPS - 1) / FD_WARPS : 0;
+    // Of this step's inputs only q and the newest key (position pos, written by the kernel before) depend on
+    // the predecessor; the positions and tables were copied in before the step's first kernel.  A block whose
+    // keys are all older starts its copies before it waits.  (Were there earlier tokens of the same sequence
+    // in this step, their keys would be new too: then the token is not its sequence's first row.)
+    const bool old_keys_only = hi <= pos && (t == 0 || tok_seq[t - 1] != b);
+    if (old_keys_only) {
 #pragma unroll
-    for (int i = 0; i < FD_STAGES - 1; ++i) issue(i);
+        for (int i = 0; i < FD_STAGES - 1; ++i) issue(i);
+    }
+    pdl_wait();
+    pdl_launch();
+    if (!old_keys_only) {
+#pragma unroll
+        for (int i = 0; i < FD_STAGES - 1; ++i) issue(i);
+    }
+
+    // Q fragments: rows = q heads of this group (rows >= n_rep are zero)
+    uint32_t qf[KS][4];
+    {
+        const bf16* q0 = q + ((size_t)t * nh + (size_t)g * n_rep) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int d = ks * 16 + 2 * tid4;
+            qf[ks][0] = gid < n_rep ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)gid * HD + d) : 0u;
+            qf[ks][1] = gid + 8 < n_rep ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(gid + 8) * HD + d) : 0u;
+            qf[ks][2] = gid < n_rep ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)gid * HD + d + 8) : 0u;
+            qf[ks][3] = gid + 8 < n_rep ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(gid + 8) * HD + d + 8) : 0u;
+        }
+    }
+
     for (int i = 0; i < my_chunks; ++i) {
         issue(i + FD_STAGES - 1);
         fd_wait<FD_STAGES - 1>();                          // chunk i has landed
