@@ -37,7 +37,9 @@ def test_embed(dtype):
     assert int(status) == 1 and float(out[1].abs().sum()) == 0.0
 
 
-@pytest.mark.parametrize("H,out_dtype", [(1000, torch.float32), (72, torch.bfloat16), (3584, torch.bfloat16)])
+@pytest.mark.parametrize("H,out_dtype", [(1000, torch.float32), (72, torch.bfloat16), (3584, torch.bfloat16),
+                                         (896, torch.bfloat16), (5120, torch.bfloat16), (8192, torch.float32),
+                                         (8196, torch.float32), (1001, torch.bfloat16)])
 def test_rmsnorm(H, out_dtype):
     from tq_kv_b200 import kernels
     x, w = rnd(7, H, scale=3.0), rnd(H) + 1.0
@@ -169,10 +171,20 @@ def test_skinny_gemm(M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (1, 8, 8), (2048, 512, 3584), (257, 1000, 1096),
                                    (512, 4608, 3584), (100, 3584, 2048)])
-def test_gemm_tc(M, N, K):
-    """The TMA + tcgen05 product: whole tiles, ragged edges in M, N and K, a long K; tiles fewer than the SMs,
-    which the float32 products cut along K (the plain store then clears C first and sums the shares)."""
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemm_tc(M, N, K, mode):
+    """The TMA + tcgen05 product on single SMs (128-row tiles) and on pairs of SMs (cta_group::2, 256-row
+    tiles): whole tiles, ragged edges in M, N and K, a long K; tiles fewer than the SMs, which the float32
+    products cut along K (the plain store then clears C first and sums the shares)."""
     from tq_kv_b200 import kernels
+    kernels.set_gemm_tc_mode(mode)
+    try:
+        _check_gemm_tc(kernels, M, N, K)
+    finally:
+        kernels.set_gemm_tc_mode(0)
+
+
+def _check_gemm_tc(kernels, M, N, K):
     x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1), rnd(N, seed=2)
     want = x.double() @ w.double().T
     tol = 2e-6 * math.sqrt(K)
@@ -224,7 +236,8 @@ def test_decode_gemm_tc(M, N, K):
     kernels.check_tc_status()
 
 
-def test_gemm_tc_accumulate_with_a_short_last_round():
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemm_tc_accumulate_with_a_short_last_round(mode):
     """More tiles than SMs with a remainder: the residual product cuts the last round's tiles along K and the
     shares add up in C (16 x 14 = 224 tiles of 128 x 256, as o_proj at 2,048 tokens of the 7B shape)."""
     from tq_kv_b200 import kernels
@@ -232,8 +245,12 @@ def test_gemm_tc_accumulate_with_a_short_last_round():
     x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1), rnd(N, seed=2)
     base = rnd(M, N, seed=3)
     out = base.clone()
-    kernels.gemm_tc(x, w, out, bias, kernels.gemm.EPI_ACCUM)
-    kernels.check_tc_status()
+    kernels.set_gemm_tc_mode(mode)
+    try:
+        kernels.gemm_tc(x, w, out, bias, kernels.gemm.EPI_ACCUM)
+        kernels.check_tc_status()
+    finally:
+        kernels.set_gemm_tc_mode(0)
     want = base.double() + x.double() @ w.double().T + bias.double()
     close(out, want, 2e-6 * math.sqrt(K), "accumulate, split last round")
 
@@ -389,7 +406,8 @@ def _paged(k, v, nkv, hd, table_row, P=64):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,window,n_splits", [(28, 4, 128, None, 1), (28, 4, 128, None, 5),
                                                        (3, 1, 32, 100, 3), (6, 6, 48, None, 7),
-                                                       (12, 2, 96, None, 4), (32, 2, 64, 50, 2), (9, 9, 128, 1, 1)])
+                                                       (12, 2, 96, None, 4), (32, 2, 64, 50, 2), (9, 9, 128, 1, 1),
+                                                       (8, 2, 64, None, 40)])       # more splits than a warp has lanes
 @pytest.mark.parametrize("flash", [True, False])
 def test_attention_over_the_paged_cache_with_splits(dtype, nh, nkv, hd, window, n_splits, flash):
     from tq_kv_b200 import kernels

@@ -23,9 +23,15 @@
 // its TMEM, raises a bit in *status and returns: an error, not a hang.
 //
 // When the tiles do not fill the last round of the persistent blocks (224
-// tiles on 148 SMs), the residual-accumulate product cuts those last tiles
-// along K into 2 to 4 shares; the shares add into C with atomic adds, so for
-// those tiles the order of two or three float additions is not fixed.
+// tiles on 148 SMs), or are fewer than the SMs, the float32 products cut
+// those tiles along K into 2 to 8 shares; the shares meet in C through the
+// reduce-add, so for those tiles the order of the float additions is not
+// fixed.
+//
+// From 129 rows on the same product runs on pairs of SMs (gemm_tc_pair_kernel
+// below): tcgen05.mma with cta_group::2 on 256 x 256 tiles, each block of a
+// 2-block cluster holding half of A's rows and half of the B tile, which cuts
+// what an SM loads per step from 48 to 32 KB (measured: 5 % off the prefill).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -123,6 +129,78 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t m, uint32_t n) {
          | (1u << 10)           // B format bf16
          | ((n >> 3) << 17)     // N / 8
          | ((m >> 4) << 24);    // M / 16
+}
+
+// ---- the epilogue of one accumulator, one warp's 32 rows --------------------------------
+// A thread holds 32 neighbouring columns of its row; the warp lays its [32 x 32] piece into shared memory
+// (rows of 128 bytes, 16-byte chunks swizzled so that the 32 rows do not meet in a bank) and one lane hands
+// it to TMA: a store, or for the residual sum a reduce-add, which adds in the L2 without reading C into the
+// SM and is the same operation for whole tiles and for shares of K.  TMA clips rows >= M and columns >= N.
+// Two buffers per warp (st): a piece is written while the one before is on its way; `piece` counts them.
+template <int EPI, typename TO>
+__device__ __forceinline__ void tc_epilogue_item(uint32_t t_row, unsigned char* st, uint32_t& piece,
+                                                 const CUtensorMap* map_c_ptr, const float* __restrict__ bias, int n0,
+                                                 int row0, int M, int N, int part, int lane) {
+    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    const bool rows_live = row0 < M;                  // a warp whose rows all lie past M stores nothing
+#pragma unroll 1
+    for (int c = 0; c < OUT_COLS; c += 32) {
+        if (n0 + c >= N) break;
+        float v[32];
+        if (EPI == EPI_SWIGLU) {
+            float u[32];
+            tc_ld32(t_row + c, v);
+            tc_ld32(t_row + TC_BN / 2 + c, u);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = (v[j] / (1.f + expf(-v[j]))) * u[j];
+        } else {
+            tc_ld32(t_row + c, v);
+            tc_wait_ld();
+        }
+        if (bias != nullptr && part <= 0) {           // one share of a tile adds the bias
+            const int col = n0 + c + lane;
+            const float mine = col < N ? bias[col] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
+        }
+        if (!rows_live) continue;
+        unsigned char* pb = st + (piece & 1) * TC_EPI_BYTES;
+        // the piece before last used this buffer: its bytes must have been read
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+        __syncwarp();
+        if (sizeof(TO) == 4) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(pb + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                __nv_bfloat162 c2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                __nv_bfloat162 d2 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                *reinterpret_cast<uint4*>(pb + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                    make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b2),
+                               *reinterpret_cast<uint32_t*>(&c2), *reinterpret_cast<uint32_t*>(&d2));
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            if (EPI == EPI_ACCUM)
+                asm volatile(
+                    "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];\n"
+                    ::"l"(map_c_ptr), "r"(n0 + c), "r"(row0), "r"(smem_u32(pb)) : "memory");
+            else
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];\n"
+                    ::"l"(map_c_ptr), "r"(n0 + c), "r"(row0), "r"(smem_u32(pb)) : "memory");
+            asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+        }
+        ++piece;
+    }
 }
 
 // ---- the kernel -------------------------------------------------------------------
@@ -270,65 +348,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC_BN;
             const int row0 = m0 + quarter * 32;
-            const bool rows_live = row0 < M;                  // a warp whose rows all lie past M stores nothing
-#pragma unroll 1
-            for (int c = 0; c < OUT_COLS; c += 32) {
-                if (n0 + c >= N) break;
-                float v[32];
-                if (EPI == EPI_SWIGLU) {
-                    float u[32];
-                    tc_ld32(t_row + c, v);
-                    tc_ld32(t_row + TC_BN / 2 + c, u);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = (v[j] / (1.f + expf(-v[j]))) * u[j];
-                } else {
-                    tc_ld32(t_row + c, v);
-                    tc_wait_ld();
-                }
-                if (bias != nullptr && part <= 0) {           // one share of a tile adds the bias
-                    const int col = n0 + c + lane;
-                    const float mine = col < N ? bias[col] : 0.f;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
-                }
-                if (!rows_live) continue;
-                unsigned char* pb = st + (piece & 1) * TC_EPI_BYTES;
-                // the piece before last used this buffer: its bytes must have been read
-                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
-                __syncwarp();
-                if (sizeof(TO) == 4) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        *reinterpret_cast<float4*>(pb + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        __nv_bfloat162 a = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                        __nv_bfloat162 c2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-                        __nv_bfloat162 d2 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-                        *reinterpret_cast<uint4*>(pb + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
-                            make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b2),
-                                       *reinterpret_cast<uint32_t*>(&c2), *reinterpret_cast<uint32_t*>(&d2));
-                    }
-                }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                __syncwarp();
-                if (lane == 0) {
-                    if (EPI == EPI_ACCUM)
-                        asm volatile(
-                            "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];\n"
-                            ::"l"(&map_c), "r"(n0 + c), "r"(row0), "r"(smem_u32(pb)) : "memory");
-                    else
-                        asm volatile(
-                            "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];\n"
-                            ::"l"(&map_c), "r"(n0 + c), "r"(row0), "r"(smem_u32(pb)) : "memory");
-                    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
-                }
-                ++piece;
-            }
+            tc_epilogue_item<EPI, TO>(t_row, st, piece, &map_c, bias, n0, row0, M, N, part, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
@@ -342,6 +362,199 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0 && *failed && status) atomicOr(status, 2);   // a wait ran out: the result is not valid
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)(2 * TC_BN))
+                     : "memory");
+    }
+}
+
+// ---- the same product on pairs of SMs (tcgen05 cta_group::2) ------------------------------
+// A cluster of two blocks owns a 256 x 256 tile: block r of the pair holds rows 128 r .. of A and rows
+// 128 r .. of the B tile (with SwiGLU: block 0 the gate rows, block 1 the up rows), and one thread of
+// block 0 issues MMAs of M = 256 that read both blocks' shared memory and write each block's half of the
+// accumulator into its own TMEM.  Per 64 of K a block loads 32 KB instead of 48, which is what the L2 has
+// to deliver to an SM; the stages saved go into a deeper pipeline (6).
+//   full[s]       block 0's: its producer announces both blocks' bytes, both blocks' TMA loads report there
+//   empty[s]      each block's own, freed by the MMAs' commit, which is multicast to both blocks
+//   acc_full[b]   each block's own, by commit multicast
+//   acc_empty[b]  block 0's: the epilogue warps of both blocks arrive there (2 x 4)
+// Every wait is bounded as above; whatever happens, both blocks reach the cluster barrier at the end, so
+// that neither leaves while the other may still touch its shared memory or barriers.
+#define T2_STAGES 6
+#define T2_STAGE_BYTES (2 * TC_A_BYTES)   /* A: 128 x 64, B: this block's 128 x 64 */
+#define T2_SMEM_BYTES (T2_STAGES * T2_STAGE_BYTES + 1024 + 4 * 2 * TC_EPI_BYTES + 256)
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the address of a shared-memory location of block `rank` of the cluster, in the cluster's window
+__device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {     // arrives on `bar` in both blocks of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int EPI, typename TO>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_c, const float* __restrict__ bias, int M, int N, int K,
+                    int b_rows_second, int n_whole, int parts, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* staging = tiles + T2_STAGES * T2_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 4 * 2 * TC_EPI_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + T2_STAGES;
+    uint64_t* acc_full = bars + 2 * T2_STAGES;
+    uint64_t* acc_empty = bars + 2 * T2_STAGES + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * T2_STAGES + 4);
+    volatile uint32_t* failed = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                  // 0: issues the MMAs
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    const int tiles_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
+    const int tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
+    const int n_tiles = tiles_m * tiles_n;
+    const int k_all = (K + TC_BK - 1) / TC_BK;
+    const int n_items = n_whole + (n_tiles - n_whole) * parts;
+    const int k_share = (k_all + parts - 1) / parts;
+    auto item = [&](int w, int& t, int& k_lo, int& k_cnt, int& part) {
+        if (w < n_whole) { t = w; k_lo = 0; k_cnt = k_all; part = -1; return; }
+        const int r = w - n_whole;
+        t = n_whole + r / parts;
+        part = r % parts;
+        k_lo = min(k_all, part * k_share);
+        k_cnt = min(k_all, k_lo + k_share) - k_lo;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T2_STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 8);          // one arrival per epilogue warp of either block
+        }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {                                       // the same warp of both blocks: one allocation for the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * TC_BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                    // the peer's barriers exist from here on
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer (both blocks): this block's A rows and its half of the B tile ----
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = pair; w < n_items && ok; w += n_pairs) {
+                int t, k_lo, k_iters, part;
+                item(w, t, k_lo, k_iters, part);
+                const int m0 = (t % tiles_m) * 2 * TC_BM + (int)rank * TC_BM;
+                const int n0 = (t / tiles_m) * OUT_COLS;
+                const int b_row = EPI == EPI_SWIGLU ? (rank == 0 ? n0 : b_rows_second + n0) : n0 + (int)rank * (TC_BN / 2);
+                for (int i = 0; i < k_iters; ++i, ++it) {
+                    const int s = it % T2_STAGES;
+                    if (!mbar_wait(smem_u32(&empty[s]), ((it / T2_STAGES) & 1) ^ 1)) { *failed = 1; ok = false; break; }
+                    const uint32_t fb = cluster_map(smem_u32(&full[s]), 0);
+                    if (rank == 0) mbar_expect_tx(smem_u32(&full[s]), 2 * T2_STAGE_BYTES);
+                    const uint32_t a_dst = smem_u32(tiles + s * T2_STAGE_BYTES);
+                    const int kc = (k_lo + i) * TC_BK;
+                    tma_load_2d_pair(a_dst, &map_a, kc, m0, fb);
+                    tma_load_2d_pair(a_dst + TC_A_BYTES, &map_b, kc, b_row, fb);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (block 0 only): D[256 x 256] over both blocks ----
+            const uint32_t idesc = instr_desc(2 * TC_BM, TC_BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int w = pair; w < n_items && ok; w += n_pairs, ++local) {
+                int t, k_lo, k_iters, part;
+                item(w, t, k_lo, k_iters, part);
+                const uint32_t buf = local & 1;
+                if (!mbar_wait(smem_u32(&acc_empty[buf]), ((local >> 1) & 1) ^ 1)) { *failed = 1; ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                for (int i = 0; i < k_iters; ++i, ++it) {
+                    const int s = it % T2_STAGES;
+                    if (!mbar_wait(smem_u32(&full[s]), (it / T2_STAGES) & 1)) { *failed = 1; ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + s * T2_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + TC_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tc_mma_pair(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                                    (i > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_pair(smem_u32(&empty[s]));        // frees the stage in both blocks
+                }
+                if (ok) tc_commit_pair(smem_u32(&acc_full[buf]));
+            }
+        }
+    } else {
+        // ---- epilogue warps (both blocks): this block's 128 rows of the tile ----
+        const int quarter = warp & 3;
+        unsigned char* st = staging + (warp - 2) * 2 * TC_EPI_BYTES;
+        uint32_t local = 0, piece = 0;
+        bool ok = true;
+        for (int w = pair; w < n_items && ok; w += n_pairs, ++local) {
+            int t, k_lo, k_iters, part;
+            item(w, t, k_lo, k_iters, part);
+            const int m0 = (t % tiles_m) * 2 * TC_BM + (int)rank * TC_BM, n0 = (t / tiles_m) * OUT_COLS;
+            const uint32_t buf = local & 1;
+            if (!mbar_wait(smem_u32(&acc_full[buf]), (local >> 1) & 1, true)) { *failed = 1; ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC_BN;
+            tc_epilogue_item<EPI, TO>(t_row, st, piece, &map_c, bias, n0, m0 + quarter * 32, M, N, part, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n"
+                             ::"r"(cluster_map(smem_u32(&acc_empty[buf]), 0)) : "memory");
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                    // nobody leaves while its peer may still need it
+    if (threadIdx.x == 0 && *failed && status) atomicOr(status, 2);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)(2 * TC_BN))
                      : "memory");
     }
 }
@@ -427,6 +640,43 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     return tq_launch_status();
 }
 
+// The pair form: 256-row tiles on clusters of two blocks.
+template <int EPI, typename TO>
+static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const float* bias, int M,
+                          int N, int K, int b_rows_second, int* status, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             T2_SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    const int n_tiles = ((N + OUT_COLS - 1) / OUT_COLS) * ((M + 2 * TC_BM - 1) / (2 * TC_BM));
+    const int pairs = tc_sm_count() / 2 > 0 ? tc_sm_count() / 2 : 1;
+    int n_whole = n_tiles, parts = 1;
+    if (EPI == EPI_ACCUM) parts = tc_last_round_parts(n_tiles, pairs, K, nullptr);
+    if (parts > 1) n_whole = n_tiles - n_tiles % pairs;
+    const int n_items = n_whole + (n_tiles - n_whole) * parts;
+    const int grid = 2 * (n_items < pairs ? n_items : pairs);
+    gemm_tc_pair_kernel<EPI, TO><<<grid, TC_THREADS, T2_SMEM_BYTES, stream>>>(ma, mb, mc, bias, M, N, K, b_rows_second,
+                                                                             n_whole, parts, status);
+    return tq_launch_status();
+}
+
+// 0: pairs of SMs for products of more than 128 rows, single SMs otherwise; 1: single SMs always; 2: pairs always.
+// Starts from the environment variable TQ_GEMM_TC_MODE (a tuning aid), else 0.
+static int g_tc_mode = -1;
+TQ_API void tq_gemm_tc_mode(int mode) { g_tc_mode = mode; }
+static int tc_mode() {
+    if (g_tc_mode < 0) {
+        const char* e = getenv("TQ_GEMM_TC_MODE");
+        g_tc_mode = e ? atoi(e) : 0;
+        if (g_tc_mode < 0 || g_tc_mode > 2) g_tc_mode = 0;
+    }
+    return g_tc_mode;
+}
+
 // A [M, K] and B [N, K] (or [2N, K] with epilogue 2) bfloat16 with row strides
 // lda / ldb (elements, multiples of 8; bases 16-byte aligned); C [M, N] with
 // row stride ldc (base and row stride in bytes multiples of 16), float32 or
@@ -447,20 +697,24 @@ TQ_API int tq_gemm_tc(const void* A, const void* B, const float* bias, void* C, 
     CUtensorMap ma, mb;
     int st = make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM);
     if (st) return st;
+    const bool pair = tc_mode() == 2 || (tc_mode() == 0 && M > TC_BM);
     const uint64_t b_rows = epilogue == EPI_SWIGLU ? 2ull * N : (uint64_t)N;
-    st = make_map(&mb, B, b_rows, (uint64_t)K, (uint64_t)ldb, epilogue == EPI_SWIGLU ? TC_BN / 2 : TC_BN);
+    // a block loads 128 rows of B at a time in the pair form and with SwiGLU, else the tile's 256
+    st = make_map(&mb, B, b_rows, (uint64_t)K, (uint64_t)ldb, (pair || epilogue == EPI_SWIGLU) ? TC_BN / 2 : TC_BN);
     if (st) return st;
     CUtensorMap mc;
     st = make_map_c(&mc, C, c_dtype == TQ_F32, (uint64_t)M, (uint64_t)N, (uint64_t)ldc);
     if (st) return st;
-#define TQ_TC(E, T) return launch_tc<E, T>(ma, mb, mc, bias, M, N, K, N, status, stream)
+#define TQ_TC(E, T)                                                                                   \
+    return pair ? launch_tc_pair<E, T>(ma, mb, mc, bias, M, N, K, N, status, stream)                  \
+                : launch_tc<E, T>(ma, mb, mc, bias, M, N, K, N, status, stream)
     if (epilogue == EPI_STORE && c_dtype == TQ_F32) {
         // A float32 result whose tiles fill the last round badly (few rows: 72 tiles on 148 SMs) is cleared and
         // then summed from shares of K like the residual product; worth it when the last round is most of the
         // work and the shares cut it by a third or more.
-        const int n_tiles = ((N + TC_BN - 1) / TC_BN) * ((M + TC_BM - 1) / TC_BM);
+        const int n_tiles = ((N + TC_BN - 1) / TC_BN) * ((M + (pair ? 2 : 1) * TC_BM - 1) / ((pair ? 2 : 1) * TC_BM));
         double gain = 1.0;
-        const int sms = tc_sm_count();
+        const int sms = pair ? tc_sm_count() / 2 : tc_sm_count();
         if (n_tiles < 2 * sms && tc_last_round_parts(n_tiles, sms, K, &gain) > 1 && gain <= 0.67) {
             cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream);
             if (e != cudaSuccess) return (int)e;

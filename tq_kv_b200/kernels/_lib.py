@@ -101,6 +101,7 @@ _SIGNATURES = {
                        c_int, c_int, c_void_p],
     "tq_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_void_p, c_void_p],
+    "tq_gemm_tc_mode": [c_int],
     "tq_decode_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_void_p, c_void_p],
     "tq_flash_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,

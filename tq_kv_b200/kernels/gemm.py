@@ -8,8 +8,8 @@
     TMA-fed (csrc/decode_gemm_tc.cu);
   * up to 16 rows of anything else: the float32 row kernel of csrc/gemm.cu
     with the same epilogues;
-  * many rows, bfloat16 × bfloat16: the TMA + tcgen05 kernel of
-    csrc/gemm_tc.cu with the same fused epilogues; with USE_TCGEN05 off, the
+  * many rows, bfloat16 × bfloat16: the TMA + tcgen05 kernels of
+    csrc/gemm_tc.cu (pairs of SMs from 129 rows on) with the same fused epilogues; with USE_TCGEN05 off, the
     library matrix product (cuBLAS through torch.mm with float32 output), as
     the reference engine does for all its products
     (src/models/turbo_generic.rs:68-91 -> candle -> cuBLAS);
@@ -43,6 +43,14 @@ def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
 # ---- tcgen05 + TMA product for many rows (csrc/gemm_tc.cu) -----------------------
 USE_TCGEN05 = True                  # False: the library product (cuBLAS) takes the many-row bfloat16 case
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
+
+
+def set_gemm_tc_mode(mode: int) -> None:
+    """0: products of more than 128 rows run on pairs of SMs (tcgen05 cta_group::2, 256-row tiles), smaller
+    ones on single SMs; 1: single SMs always; 2: pairs always.  The default is 0 (or TQ_GEMM_TC_MODE)."""
+    if mode not in (0, 1, 2):
+        raise KernelError(f"gemm_tc mode {mode}: 0, 1 or 2")
+    core().tq_gemm_tc_mode(mode)
 
 
 def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE):
