@@ -119,10 +119,12 @@ static inline int tq_launch_status() { return (int)cudaGetLastError(); }
 // successor start early in turn.  Without the launch attribute both
 // instructions do nothing.
 //
-// Measured on decode steps by kernel family: every family gains a little or
-// nothing alone, the attention merge loses, and all but the merge together
-// gain 2 to 3 % on the 7B shape and 3 to 14 % on the 0.5B shape, whose step is
-// mostly launch latency.  So that is the default.  TQ_PDL=0 switches it off,
+// Measured on decode steps: together the families gain 3 to 9 % on the 7B
+// shape and up to 14 % on the 0.5B shape, whose step is mostly launch latency.
+// One thing loses: a kernel let in while the decode attention streams the
+// cache (2 to 4 % of the step), whichever kernel that is; so flash_decode
+// waits but never calls pdl_launch(), and the merge that follows it, which
+// then has nothing to gain, is left out of the default.  TQ_PDL=0 switches it off,
 // TQ_PDL=1 on for every family, a larger number is a mask of families:
 // 2 element-wise, 4 skinny_gemm, 8 decode_gemm_tc, 16 flash_decode,
 // 32 attention merge, 64 sampling.  Every launch names its family.

@@ -116,8 +116,9 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
 #pragma unroll
         for (int i = 0; i < FD_STAGES - 1; ++i) issue(i);
     }
+    // No pdl_launch(): a kernel let in while this one streams the cache only gets in its way (measured: the
+    // step is 2 to 4 % slower at batch 8 and 64); the next kernel starts when this one has ended.
     pdl_wait();
-    pdl_launch();
     if (!old_keys_only) {
 #pragma unroll
         for (int i = 0; i < FD_STAGES - 1; ++i) issue(i);
