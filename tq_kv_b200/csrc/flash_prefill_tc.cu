@@ -302,18 +302,22 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
             for (int c = 0; c < FT_BN; c += 32) ft_ld32_issue(s_addr + c, sv + c);
             ft_ld_wait();
-            float mx = -INFINITY;
-            if (inside) {
-#pragma unroll
-                for (int j = 0; j < FT_BN; ++j) mx = fmaxf(mx, sv[j]);
-            } else {
+            if (!inside) {
 #pragma unroll
                 for (int j = 0; j < FT_BN; ++j) {
                     const int key = j0 + j;
-                    if (key >= j_lo && key <= j_hi) mx = fmaxf(mx, sv[j]);
-                    else sv[j] = -INFINITY;                    // a masked key: 2^-inf = 0 below
+                    if (key < j_lo || key > j_hi) sv[j] = -INFINITY;     // a masked key: 2^-inf = 0 below
                 }
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four chains instead of one of 64
+#pragma unroll
+            for (int j = 0; j < FT_BN; j += 4) {
+                mx4[0] = fmaxf(mx4[0], sv[j]);
+                mx4[1] = fmaxf(mx4[1], sv[j + 1]);
+                mx4[2] = fmaxf(mx4[2], sv[j + 2]);
+                mx4[3] = fmaxf(mx4[3], sv[j + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_tile = mx * scale_log2;
             // P of the tile before and O are in use until that tile's P·V is done
             if (it > 0 && !ft_wait(ft_smem(p_empty), (it - 1) & 1, true)) { *failed = 1; ok = false; break; }
@@ -335,7 +339,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             // a row that has seen no key yet keeps m_ref = -inf; its scores are all masked (-inf) and must
             // give 0, not 2^(-inf + inf)
             const float neg_ref = m_ref > -INFINITY ? -m_ref : 0.f;
-            float rs = 0.f;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};                // partial sums by chunk, so that the adds overlap
             unsigned char* prow = p_s + r * 128;
 #pragma unroll
             for (int c = 0; c < FT_BN; c += 8) {              // 8 keys = one 16-byte chunk of the swizzled row
@@ -344,14 +348,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 for (int j = 0; j < 8; j += 2) {
                     const float p0 = ft_exp2(fmaf(sv[c + j], scale_log2, neg_ref));
                     const float p1 = ft_exp2(fmaf(sv[c + j + 1], scale_log2, neg_ref));
-                    rs += p0 + p1;
+                    rs4[(c >> 3) & 3] += p0 + p1;
                     __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                     packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
                 }
                 *reinterpret_cast<uint4*>(prow + (((c >> 3) ^ (r & 7)) << 4)) =
                     make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            l_run += rs;
+            l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P is read by the tensor core
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             ft_arrive(ft_smem(p_full));
