@@ -392,6 +392,40 @@ def test_attention_over_packed_prompts(dtype, nh, nkv, hd, window, lens, flash, 
         close(out[a:e], want, 2e-6 if dtype == torch.float32 else 8e-3, f"row {b}")
 
 
+def test_tcgen05_prompt_attention_under_load_agrees_with_the_mma_kernel(monkeypatch):
+    """A full machine of long chains (40 q heads, eight prompts of 2,048 tokens: 5,120 blocks of up to 32 key
+    tiles), several times over: buffers in tensor memory are reused tile after tile, and a mistake in the order
+    of the MMAs and waits that share them shows only under load and only sometimes (two such mistakes were
+    found this way).  The mma.sync kernel is the reference here (checked against the plain attention above);
+    every run must agree with it."""
+    from tq_kv_b200 import kernels
+    import importlib
+    att = importlib.import_module("tq_kv_b200.kernels.attention")
+    nh, nkv, hd, lens = 40, 8, 128, [2048] * 8
+    T = sum(lens)
+    cu = (torch.arange(9, device=DEV) * 2048).int()
+    tok_seq = torch.arange(8, device=DEV).repeat_interleave(2048).int()
+    tok_pos = torch.arange(2048, device=DEV).repeat(8).int()
+    start = torch.zeros(8, dtype=torch.int32, device=DEV)
+
+    def run(q, k, v, tc):
+        monkeypatch.setattr(att, "USE_TC_ATTENTION", tc)
+        out = torch.empty_like(q)
+        kernels.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd, tok_pos=tok_pos, tok_seq=tok_seq,
+                          cu_seqlens=cu, start_pos=start, window=None, k_packed=k, v_packed=v)
+        return out
+
+    for rep in range(6):
+        q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=10 * rep)
+        k = rnd(T, nkv * hd, dtype=torch.bfloat16, seed=10 * rep + 1)
+        v = rnd(T, nkv * hd, dtype=torch.bfloat16, seed=10 * rep + 2)
+        want = run(q, k, v, False).float()
+        got = run(q, k, v, True).float()
+        kernels.check_tc_status()
+        assert torch.isfinite(got).all(), f"run {rep}: non-finite output"
+        assert float((got - want).abs().max()) <= 8e-3, f"run {rep}: {float((got - want).abs().max()):.3e}"
+
+
 def _paged(k, v, nkv, hd, table_row, P=64):
     """Scatters [Tk, nkv*hd] keys/values into pages per `table_row`."""
     n_pages = max(table_row) + 2

@@ -56,3 +56,33 @@ def test_real_layer_sizes_whole_then_decoded_and_batched(tmp_root, shape, layers
                     live.remove(i)
         del eng
         torch.cuda.empty_cache()
+
+
+def test_eight_long_prompts_at_the_32b_shape_under_both_prompt_attention_kernels(monkeypatch):
+    """Eight prompts of 2,048 tokens through two layers of the 32B shape (40 q heads: 5,120 attention blocks, the
+    longest with 32 key tiles; scores with the spread that real projections give them), several times: the
+    logits at the prompts' ends must be finite and agree between the tcgen05 attention and the mma.sync
+    attention.  A mistake in the tcgen05 kernel's reuse of tensor memory showed only here, and not every time."""
+    import importlib
+    import tq_kv_b200 as tq
+    from tq_kv_b200.engine import Engine, StepRow
+    att = importlib.import_module("tq_kv_b200.kernels.attention")
+    cfg = dict(tq.named_shape("qwen2.5-32b"))
+    cfg.update(num_hidden_layers=2, max_window_layers=2, vocab_size=VOCAB)
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_slots=8, max_context=2048)
+    prompts = [random_tokens(2048, VOCAB, 500 + i) for i in range(8)]
+
+    def run(tc):
+        monkeypatch.setattr(att, "USE_TC_ATTENTION", tc)
+        slots = [eng.new_sequence() for _ in prompts]
+        out = eng.step([StepRow(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        for s in slots:
+            eng.release(s)
+        return out.float().cpu()
+
+    want = run(False)
+    assert torch.isfinite(want).all()
+    for rep in range(4):
+        got = run(True)
+        assert torch.isfinite(got).all(), f"run {rep}: non-finite logits in rows {(~torch.isfinite(got)).any(1).nonzero().flatten().tolist()}"
+        assert float((got - want).abs().max()) <= 0.03 * max(1.0, float(want.abs().max())), f"run {rep}"
