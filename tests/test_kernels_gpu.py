@@ -255,6 +255,36 @@ def test_gemm_tc_accumulate_with_a_short_last_round(mode):
     close(out, want, 2e-6 * math.sqrt(K), "accumulate, split last round")
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemm_tc_under_load(mode):
+    """Thousands of tiles per launch, several launches: every block walks many tiles through its stages, its two
+    accumulators and its epilogue buffers, which is where a mistake in the order of waits would show."""
+    from tq_kv_b200 import kernels
+    M, K = 8192, 5120
+    x = rnd(M, K, dtype=torch.bfloat16)
+    kernels.set_gemm_tc_mode(mode)
+    try:
+        for rep in range(2):
+            for N, epi in ((5120, kernels.gemm.EPI_ACCUM), (7168, kernels.gemm.EPI_STORE), (6912, kernels.gemm.EPI_SWIGLU)):
+                rows = 2 * N if epi == kernels.gemm.EPI_SWIGLU else N
+                w = rnd(rows, K, dtype=torch.bfloat16, seed=7 * rep + N, scale=1.0 / math.sqrt(K))
+                y = x.float() @ w.float().T
+                if epi == kernels.gemm.EPI_ACCUM:
+                    base = rnd(M, N, seed=3)
+                    out, want, tol = base.clone(), base + y, 2e-4
+                elif epi == kernels.gemm.EPI_STORE:
+                    out, want, tol = torch.full((M, N), 7.0, device=DEV), y, 2e-4
+                else:
+                    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+                    want, tol = torch.nn.functional.silu(y[:, :N]) * y[:, N:], 4e-2
+                kernels.gemm_tc(x, w, out, None, epi)
+                kernels.check_tc_status()
+                err = float((out.float() - want).abs().max())
+                assert err <= tol, f"mode {mode}, N {N}, epilogue {epi}, launch {rep}: {err:.3e}"
+    finally:
+        kernels.set_gemm_tc_mode(0)
+
+
 def test_a_wait_that_ran_out_is_reported_by_the_host_check():
     """The tcgen05 kernels bound every mbarrier wait and raise a status bit instead of hanging.  No wait is made
     to run out here (that would need a kernel that misbehaves on purpose); the status word is set by hand and the
