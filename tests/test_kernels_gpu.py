@@ -446,14 +446,18 @@ def test_tcgen05_prompt_attention_under_load_agrees_with_the_mma_kernel(monkeypa
         return out
 
     for rep in range(6):
-        q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=10 * rep)
+        # every other run with a wide spread of scores: rows' maxima then grow late and by a lot, and the
+        # blocks' warps take different paths (rescaling the output or not) at different speeds
+        q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=10 * rep, scale=3.0 if rep % 2 else 1.0)
         k = rnd(T, nkv * hd, dtype=torch.bfloat16, seed=10 * rep + 1)
         v = rnd(T, nkv * hd, dtype=torch.bfloat16, seed=10 * rep + 2)
         want = run(q, k, v, False).float()
         got = run(q, k, v, True).float()
         kernels.check_tc_status()
         assert torch.isfinite(got).all(), f"run {rep}: non-finite output"
-        assert float((got - want).abs().max()) <= 8e-3, f"run {rep}: {float((got - want).abs().max()):.3e}"
+        # both are rounded to bfloat16 at the end: a step of 2^-8 of the value, beside the 8e-3 of the small values
+        excess = (got - want).abs() - (8e-3 + 2.0 ** -6 * want.abs())
+        assert float(excess.max()) <= 0, f"run {rep}: {float((got - want).abs().max()):.3e}"
 
 
 def _paged(k, v, nkv, hd, table_row, P=64):

@@ -7,10 +7,11 @@
 //                     buffers, so the next tile's product is issued while this
 //                     tile's softmax runs;
 //   softmax           four warps, one query row per thread (TMEM lane = row, so
-//                     the row maximum and sum need no shuffles), float32; P is
-//                     written to shared memory as bfloat16 in the swizzled
-//                     K-major layout the next MMA reads;
-//   O += P · V        tcgen05.mma with V as an MN-major operand (the V tile is
+//                     the row maximum and sum need no shuffles), float32; P goes
+//                     back into TMEM as bfloat16, over the scores it came from
+//                     (tcgen05.st; a 32-bit column holds two neighbouring keys);
+//   O += P · V        tcgen05.mma with P as the A operand from TMEM and V as an
+//                     MN-major operand from shared memory (the V tile is
 //                     [keys][head_dim] as it lies in memory), accumulated in TMEM
 //                     over all tiles and read once at the end.
 // P and O are scaled against a reference maximum per row that moves only when
@@ -20,13 +21,23 @@
 // exponentials stay below 2^8.
 // Roles: warp 0 lane 0 issues TMA loads (Q once, K/V tiles through two stages),
 // warp 1 lane 0 issues the MMAs, warps 2..5 do the softmax and the final store.
-// A block takes half an SM's shared memory and half its TMEM: two blocks share
+// A block takes 96 KB of shared memory and half an SM's TMEM: two blocks share
 // an SM, and one's tensor-core work runs under the other's softmax.  Blocks
 // with the most key tiles start first.  Keys and values come from the step's
 // packed rows (PAGED = false) or from the paged cache (one 64-token page per
 // tile).  An optional sliding window narrows the key range; tiles outside a
 // block's range are never loaded.  All mbarrier waits are bounded (see
 // gemm_tc.cu).
+//
+// Order between the threads, beyond the producer/consumer pairs: the MMA
+// thread waits for the P·V of the tile before (p_empty) before it issues the
+// Q·K^T of the tile after, which writes over that tile's P; a softmax thread
+// waits for the phase of p_full before its own before it arrives again (it may
+// be a whole tile ahead of the slowest thread, and a second arrival in the
+// same phase would stand in for the slow thread's first); the end of the last
+// P·V has a barrier of its own (o_done), since the softmax threads follow
+// p_empty only when they rescale O and a wait by parity cannot tell a phase
+// that is two behind from one that is done.  Two load tests guard this.
 //
 // Formulas: src/models/turbo_generic.rs:1620-1631 (see attention.cu).
 #include <cuda.h>
@@ -36,7 +47,7 @@
 #define FT_BM 128
 #define FT_BN 64
 #define FT_THREADS 192
-#define FT_SUB_BYTES (128 * 128)          // a [128 rows x 64 bf16] sub-tile (Q, P)
+#define FT_SUB_BYTES (128 * 128)          // a [128 rows x 64 bf16] sub-tile (Q)
 #define FT_KV_SUB_BYTES (FT_BN * 128)     // a [64 keys x 64 bf16] sub-tile (K, V)
 #define FT_WAIT_CYCLES (4000000000ll)
 
@@ -75,6 +86,14 @@ __device__ __forceinline__ void ft_mma(uint32_t d, uint64_t a, uint64_t b, uint3
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
         ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+// the same with the A operand in tensor memory (lane = row, a 32-bit column holds two neighbouring bfloat16 of K)
+__device__ __forceinline__ void ft_mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
 __device__ __forceinline__ void ft_ld32(uint32_t taddr, float* v) {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
@@ -152,8 +171,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     unsigned char* q_s = smem_raw;
     unsigned char* k_s = q_s + Q_BYTES;                    // [2 stages]
     unsigned char* v_s = k_s + 2 * KV_BYTES;               // [2 stages]
-    unsigned char* p_s = v_s + 2 * KV_BYTES;               // P: [128 rows x 64 keys]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + FT_SUB_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * KV_BYTES);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;                           // [2]  K and V have rings of their own: a K stage is
     uint64_t* k_empty = bars + 3;                          // [2]  free as soon as its Q·K^T is done, long before
@@ -161,8 +179,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     uint64_t* v_empty = bars + 7;                          // [2]  next has a whole iteration to arrive
     uint64_t* s_full = bars + 9;                           // [2]
     uint64_t* p_full = bars + 11;                          // 128 arrivals (softmax threads)
-    uint64_t* p_empty = bars + 12;                         // the P·V of a tile is done: P and O may be touched
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    uint64_t* p_empty = bars + 12;                         // the P·V of a tile is done: O may be touched
+    uint64_t* o_done = bars + 13;                          // once: the last P·V is done, O is final
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile uint32_t* failed = tmem_slot + 1;
 
     // which (sequence, 128-token tile) is this block's?  Later tiles of a sequence have more keys to walk:
@@ -194,6 +213,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;\n" ::"r"(ft_smem(p_full)));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(p_empty)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(o_done)));
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -247,7 +267,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                                      ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
             bool ok = ft_wait(ft_smem(q_full), 0);
             if (!ok) *failed = 1;
-            const uint32_t qa = ft_smem(q_s), pa = ft_smem(p_s);
+            const uint32_t qa = ft_smem(q_s);
             auto issue_qk = [&](int it) -> bool {            // S[it & 1] = Q · K(it)^T over head_dim
                 const int s = it & 1;
                 if (!ft_wait(ft_smem(&k_full[s]), (it >> 1) & 1)) return false;
@@ -264,7 +284,13 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if (ok && !issue_qk(0)) { *failed = 1; ok = false; }
             for (int it = 0; it < n_tiles && ok; ++it) {
                 const int s = it & 1;
-                // the next tile's scores are computed while the softmax threads work on this one
+                // The next tile's scores are computed while the softmax threads work on this one.  They go
+                // into the buffer that holds the P of the tile before, which that tile's P·V reads as its A
+                // operand from tensor memory; nothing documented orders a later MMA's writes behind an earlier
+                // MMA's operand reads there, so that P·V has to be complete first.  The same wait keeps the
+                // softmax threads within one phase of p_empty, which their wait by parity (when they rescale O)
+                // relies on.
+                if (it > 0 && !ft_wait(ft_smem(p_empty), (it - 1) & 1)) { *failed = 1; ok = false; break; }
                 if (it + 1 < n_tiles && !issue_qk(it + 1)) { *failed = 1; ok = false; break; }
                 if (!ft_wait(ft_smem(&v_full[s]), (it >> 1) & 1) || !ft_wait(ft_smem(p_full), it & 1)) {
                     *failed = 1; ok = false; break;
@@ -272,11 +298,12 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t va = ft_smem(v_s + s * KV_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < FT_BN / 16; ++ks)      // O += P · V over the tile's 64 keys
-                    ft_mma(tmem_o, ft_desc_k(pa + ks * 32), ft_desc_mn(va + ks * 2048, FT_KV_SUB_BYTES), idesc_o,
-                           (it > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < FT_BN / 16; ++ks)      // O += P · V over the tile's 64 keys; P sits where S was
+                    ft_mma_ts(tmem_o, tmem_s + s * FT_BN + ks * 8, ft_desc_mn(va + ks * 2048, FT_KV_SUB_BYTES),
+                              idesc_o, (it > 0 || ks > 0) ? 1u : 0u);
                 ft_commit(ft_smem(&v_empty[s]));             // the stage is free once these MMAs are done
                 ft_commit(ft_smem(p_empty));
+                if (it == n_tiles - 1) ft_commit(ft_smem(o_done));
             }
         }
     } else {
@@ -319,11 +346,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_tile = mx * scale_log2;
-            // P of the tile before and O are in use until that tile's P·V is done
-            if (it > 0 && !ft_wait(ft_smem(p_empty), (it - 1) & 1, true)) { *failed = 1; ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const bool grow = m_tile > m_ref + 8.f;          // also true for the first finite maximum
             if (__any_sync(0xffffffffu, grow) && it > 0) {
+                // O is in use until the P·V of the tile before is done
+                if (!ft_wait(ft_smem(p_empty), (it - 1) & 1, true)) { *failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const float f = grow ? exp2f(m_ref - m_tile) : 1.f;      // exp2(-inf) = 0: nothing was summed yet
 #pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
@@ -340,28 +367,32 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             // give 0, not 2^(-inf + inf)
             const float neg_ref = m_ref > -INFINITY ? -m_ref : 0.f;
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};                // partial sums by chunk, so that the adds overlap
-            unsigned char* prow = p_s + r * 128;
+            // P goes back into tensor memory, over the scores it came from: a 32-bit column holds two
+            // neighbouring keys as bfloat16, the layout the next MMA takes its A operand in.  That buffer is
+            // free: the Q·K^T that wrote these scores was issued only after the P·V that read the P before last
+            // from it had completed.
+            float packed[FT_BN / 2];
 #pragma unroll
-            for (int c = 0; c < FT_BN; c += 8) {              // 8 keys = one 16-byte chunk of the swizzled row
-                uint32_t packed[4];
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    const float p0 = ft_exp2(fmaf(sv[c + j], scale_log2, neg_ref));
-                    const float p1 = ft_exp2(fmaf(sv[c + j + 1], scale_log2, neg_ref));
-                    rs4[(c >> 3) & 3] += p0 + p1;
-                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                    packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
-                }
-                *reinterpret_cast<uint4*>(prow + (((c >> 3) ^ (r & 7)) << 4)) =
-                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            for (int j = 0; j < FT_BN; j += 2) {
+                const float p0 = ft_exp2(fmaf(sv[j], scale_log2, neg_ref));
+                const float p1 = ft_exp2(fmaf(sv[j + 1], scale_log2, neg_ref));
+                rs4[(j >> 1) & 3] += p0 + p1;
+                __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                packed[j >> 1] = __uint_as_float(*reinterpret_cast<uint32_t*>(&pk));
             }
+            ft_st32(s_addr, packed);
             l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P is read by the tensor core
+            // A thread that is a whole tile ahead of the slowest must not arrive again before the phase of the
+            // tile before is complete: its second arrival would stand in for the slow thread's first, and the
+            // P·V would start without that thread's rows of P.  (While P went through shared memory, waiting for
+            // the P·V of the tile before kept the threads together.)
+            if (it > 0 && !ft_wait(ft_smem(p_full), (it - 1) & 1, true)) { *failed = 1; ok = false; break; }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             ft_arrive(ft_smem(p_full));
         }
-        // the last tile's P·V, then O / l
-        if (ok && !ft_wait(ft_smem(p_empty), (n_tiles - 1) & 1, true)) { *failed = 1; ok = false; }
+        // The last tile's P·V, then O / l.  (A barrier of its own: the softmax threads no longer follow every
+        // phase of p_empty, and a wait by parity cannot tell a phase that is two behind from one that is done.)
+        if (ok && !ft_wait(ft_smem(o_done), 0, true)) { *failed = 1; ok = false; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (ok) {
             const float inv = 1.f / l_run;
@@ -410,7 +441,7 @@ static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
                      int table_width, int ring_pages, const int* cu_seqlens, const int* start_pos, int n_seqs,
                      int n_tokens, int window, float scale, bf16* out, int nh, int nkv, int* status,
                      cudaStream_t stream) {
-    constexpr int SMEM = (HD / 64) * (FT_SUB_BYTES + 4 * FT_KV_SUB_BYTES) + FT_SUB_BYTES + 256;
+    constexpr int SMEM = (HD / 64) * (FT_SUB_BYTES + 4 * FT_KV_SUB_BYTES) + 256;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD, PAGED>,
