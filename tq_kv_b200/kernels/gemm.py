@@ -1,11 +1,12 @@
 """Matrix products: y = x · W^T with W stored [out, in].
 
 `linear()` picks the kernel from the operands:
-  * up to 16 rows of bfloat16 (decoding): the weight-streaming mma.sync
-    kernel of csrc/skinny_gemm.cu, which reads the weight once and fuses bias,
-    SwiGLU gating and the float32 accumulation into the residual stream;
-  * 17 to 64 rows of bfloat16: the same job on tcgen05 with swapped operands,
-    TMA-fed (csrc/decode_gemm_tc.cu);
+  * up to 16 rows of bfloat16 and weights under 24 MB (decoding a small
+    model): the weight-streaming mma.sync kernel of csrc/skinny_gemm.cu, which
+    reads the weight once and fuses bias, SwiGLU gating and the float32
+    accumulation into the residual stream;
+  * up to 64 rows of bfloat16 otherwise: the same job on tcgen05 with swapped
+    operands, TMA-fed (csrc/decode_gemm_tc.cu);
   * up to 16 rows of anything else: the float32 row kernel of csrc/gemm.cu
     with the same epilogues;
   * many rows, bfloat16 × bfloat16: the TMA + tcgen05 kernels of
@@ -27,7 +28,7 @@ from ._lib import KernelError, check, check_tc_status, core, dtype_code, need_co
 
 ROW_KERNEL_MAX_ROWS = 16
 SKINNY_MAX_ROWS = 64
-TC_DECODE_MIN_WEIGHT_BYTES = 64 << 20
+TC_DECODE_MIN_WEIGHT_BYTES = 24 << 20      # see linear()
 
 
 def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
@@ -137,8 +138,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
     if M == 0:
         return out
 
-    # decoding: the TMA-fed tcgen05 kernel for batches over 16 rows and for large weights at any batch (measured
-    # faster from about 64 MB of weight on), the mma.sync kernel for small weights at small batches
+    # decoding: the TMA-fed tcgen05 kernel for batches over 16 rows and for weights from 24 MB on at any batch,
+    # the mma.sync kernel for smaller weights at small batches.  The limit was set inside the whole decode step
+    # (the 7B shape's 26 and 33 MB products are 4 % of a step faster on the TMA kernel, the 0.5B shape's 9 and
+    # 17 MB products 5 % slower); timed alone, back to back, the mma.sync kernel looks faster up to 64 MB.
     if (USE_TCGEN05 and M <= SKINNY_MAX_ROWS and _tc_ok(x, w, out, swiglu)
             and (not accumulate or out.dtype == torch.float32)
             and (M > ROW_KERNEL_MAX_ROWS or w.numel() * 2 >= TC_DECODE_MIN_WEIGHT_BYTES or not _skinny_ok(x, w))):
