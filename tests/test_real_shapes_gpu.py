@@ -115,3 +115,35 @@ def test_many_decode_steps_replayed_and_launched_one_by_one_agree(shape, batch):
     scale = max(1.0, float(runs[1].abs().max()))
     err = float((runs[0] - runs[1]).abs().max())
     assert err <= 0.02 * scale, f"{shape}, batch {batch}: replayed and plain launches differ by {err:.3e}"
+
+
+def test_deterministic_switch_gives_the_same_bits_twice(tmp_path):
+    """With TQ_DETERMINISTIC=1 no product's shares of K meet in memory in arrival order: two runs of the same
+    prompt and decode steps at the 7B layer shape give identical logits (a child process each, since the switch is
+    read once)."""
+    import subprocess
+    import sys
+    script = tmp_path / "run.py"
+    script.write_text(
+        "import sys, torch\n"
+        "sys.path.insert(0, REPO); sys.path.insert(0, TESTS)\n"
+        "import tq_kv_b200 as tq\n"
+        "from tq_kv_b200.engine import Engine, StepRow\n"
+        "from helpers import random_tokens\n"
+        "cfg = dict(tq.named_shape('qwen2.5-7b')); cfg.update(num_hidden_layers=2, max_window_layers=2, vocab_size=3000)\n"
+        "eng = Engine.from_random(cfg, seed=1, dtype='bfloat16', max_slots=8, max_context=1024)\n"
+        "slots = [eng.new_sequence() for _ in range(8)]\n"
+        "outs = [eng.step([StepRow(s, random_tokens(300 + 7 * i, 3000, i), [299 + 7 * i]) for i, s in enumerate(slots)])]\n"
+        "for t in range(20):\n"
+        "    outs.append(eng.step([StepRow(s, [(5 * t + i) % 3000], [0]) for i, s in enumerate(slots)]))\n"
+        "torch.save(torch.cat(outs).cpu(), sys.argv[1])\n"
+        .replace("REPO", repr(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+        .replace("TESTS", repr(os.path.dirname(os.path.abspath(__file__)))))
+    results = []
+    for i in range(2):
+        out = tmp_path / f"out{i}.pt"
+        env = dict(os.environ, TQ_DETERMINISTIC="1")
+        subprocess.run([sys.executable, str(script), str(out)], check=True, env=env, timeout=300)
+        results.append(torch.load(out))
+    assert torch.isfinite(results[0]).all()
+    assert torch.equal(results[0], results[1])

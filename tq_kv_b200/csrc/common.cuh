@@ -108,6 +108,18 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 static inline int tq_launch_status() { return (int)cudaGetLastError(); }
 
+// TQ_DETERMINISTIC=1: no product is cut along K into shares that meet in memory in arrival order (the tcgen05
+// products then run somewhat slower: fewer blocks where tiles are few).  Every sum is then made in a fixed
+// order, and two runs of the same steps give the same bits.
+static inline bool tq_deterministic() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("TQ_DETERMINISTIC");
+        on = (e && e[0] == '1') ? 1 : 0;
+    }
+    return on == 1;
+}
+
 // ---- programmatic dependent launch -------------------------------------------
 // Kernels of a decode step are short and run back to back.  Launched with
 // this attribute, a kernel may start while its predecessor in the stream is

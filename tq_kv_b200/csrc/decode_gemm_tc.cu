@@ -405,7 +405,7 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         slots = 2 * (sms > 0 ? sms : 1);
     }
-    if (!SWIGLU && sizeof(TO) == 4 && g_force_ranks >= 0 && k_total >= 16 &&
+    if (!SWIGLU && sizeof(TO) == 4 && g_force_ranks >= 0 && k_total >= 16 && !tq_deterministic() &&
         (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (ldy & 3) == 0) {
         int splits = slots / tiles;
         if (splits > k_total / 8) splits = k_total / 8;

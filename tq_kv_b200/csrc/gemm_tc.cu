@@ -593,7 +593,7 @@ static int tc_last_round_parts(int n_tiles, int sms, int K, double* gain) {
     const int rem = n_tiles % sms, k_all = (K + TC_BK - 1) / TC_BK;
     int parts = 1;
     double best = 1.0;
-    if (rem > 0) {
+    if (rem > 0 && !tq_deterministic()) {
         for (int p = 2; p <= 8 && k_all / p >= 8; ++p) {
             const double t = (double)((rem * p + sms - 1) / sms) / p + 0.02 * p;
             if (t < best - 1e-9) { best = t; parts = p; }
