@@ -73,9 +73,10 @@ __device__ __forceinline__ void dg_ld32(uint32_t taddr, float* v) {
 }
 
 // MP: padded batch (32 or 64) = columns of the accumulator.
-// DG_STAGES: 4 (96 KB per block: two blocks fit an SM, one's epilogue runs under the other's loads) or 8.
+// DG_STAGES: 4 (96 KB per block: two blocks fit an SM, one's epilogue runs under the other's loads).  Inside the
+// decode step five stages were slower (200 KB an SM leave the next kernel no room to set itself up), eight too.
 template <int MP, bool SWIGLU, typename TO, int DG_STAGES, bool REDUCE>
-__global__ void __launch_bounds__(DG_THREADS, DG_STAGES == 4 ? 2 : 1)
+__global__ void __launch_bounds__(DG_THREADS, 2)
 decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       const __grid_constant__ CUtensorMap map_y, const float* __restrict__ bias, TO* __restrict__ Y,
                       int M, int N, int K, int ldy, int accumulate, int k_splits, int* __restrict__ status) {
@@ -162,10 +163,9 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: D[128 x MP] (+)= W_tile[128 x 64] · X_tile[MP x 64]^T ----
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MP >> 3) << 17) | ((uint32_t)(DG_ROWS >> 4) << 24);
-        bool ok = true;
         for (int i = 0; i < k_iters; ++i) {
             const int s = i % DG_STAGES;
-            if (!dg_wait(dg_smem(&full[s]), (i / DG_STAGES) & 1)) { *failed = 1; ok = false; break; }
+            if (!dg_wait(dg_smem(&full[s]), (i / DG_STAGES) & 1)) { *failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t w_addr = dg_smem(tiles + s * STAGE_BYTES);
             const uint32_t x_addr = w_addr + DG_W_BYTES;
@@ -182,7 +182,6 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                          ::"r"(dg_smem(&empty[s])) : "memory");
         }
-        (void)ok;
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                      ::"r"(dg_smem(acc_full)) : "memory");
     }
@@ -314,9 +313,6 @@ static int dg_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
-static int g_force_ranks = 0;       // tuning aids: fixed number of K shares (negative: as a cluster) / stage count
-static int g_force_stages = 0;
-TQ_API void tq_decode_gemm_tc_force(int ranks, int stages) { g_force_ranks = ranks; g_force_stages = stages; }
 
 // The REDUCE form: tiles x splits independent blocks, partial tiles summed into Y by TMA.
 template <int MP>
@@ -405,11 +401,10 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         slots = 2 * (sms > 0 ? sms : 1);
     }
-    if (!SWIGLU && sizeof(TO) == 4 && g_force_ranks >= 0 && k_total >= 16 && !tq_deterministic() &&
+    if (!SWIGLU && sizeof(TO) == 4 && k_total >= 16 && !tq_deterministic() &&
         (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (ldy & 3) == 0) {
         int splits = slots / tiles;
         if (splits > k_total / 8) splits = k_total / 8;
-        if (g_force_ranks > 0) splits = g_force_ranks;
         if (splits > 1)
             return dg_launch_reduce<MP>(mw, mx, bias, (float*)Y, M, N, K, ldy, accumulate, status, splits, stream);
     }
@@ -418,11 +413,6 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
     const int max_ranks = M > 16 ? 4 : 8, want_blocks = M > 16 ? 64 : 148;
     int ranks = 1;
     while (ranks < max_ranks && tiles * ranks < want_blocks && k_total / (ranks * 2) >= 4) ranks *= 2;
-    if (g_force_ranks > 0) ranks = g_force_ranks;
-    if (g_force_ranks < 0) ranks = -g_force_ranks;                 // negative: the cluster form with that many blocks
-    int stages = 4;
-    if (g_force_stages > 0) stages = g_force_stages;
-    if (stages == 8) return dg_launch_s<MP, SWIGLU, TO, 8>(mw, mx, bias, Y, M, N, K, ldy, accumulate, status, ranks, stream);
     return dg_launch_s<MP, SWIGLU, TO, 4>(mw, mx, bias, Y, M, N, K, ldy, accumulate, status, ranks, stream);
 }
 

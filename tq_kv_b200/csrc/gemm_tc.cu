@@ -336,7 +336,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // >= N.  Two buffers per warp: a piece is written while the one before is on its way. ----
         const int quarter = warp & 3;
         unsigned char* st = staging + (warp - 2) * 2 * TC_EPI_BYTES;
-        constexpr int ROW_BYTES = 32 * (int)sizeof(TO);       // 128 (float32) or 64 (bfloat16)
         uint32_t local = 0, piece = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
@@ -354,7 +353,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // all pieces have landed
-        (void)ROW_BYTES;
     }
     __syncwarp();
     tc_fence_before();
