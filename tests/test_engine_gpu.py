@@ -319,3 +319,23 @@ def test_an_entry_can_read_another_entrys_cache(tmp_root):
         assert_close(torch.cat(got), want, "float32", "shared cache")
     finally:
         unregister_architecture("SharedForCausalLM")
+
+
+def test_replayed_steps_read_the_kernels_status_word_now_and_then(tmp_root):
+    """Replayed decode steps do not wait for the device, so the status word of the tcgen05 kernels is read only
+    every 256 of them; a bit raised in between must still surface as an error (here raised by hand)."""
+    from tq_kv_b200 import kernels
+    from tq_kv_b200.engine import StepRow
+    eng, _ = engine_for(tmp_root, "b", "bfloat16")
+    s = eng.new_sequence()
+    eng.step([StepRow(s, [1, 2, 3], [])])
+    eng.step([StepRow(s, [4], [0])])                       # a replayed step
+    eng._replays_unchecked = 255
+    kernels._lib.tc_status_word(torch.device("cuda:0")).fill_(2)
+    try:
+        with pytest.raises(kernels.KernelError, match="wait ran out"):
+            eng.step([StepRow(s, [5], [0])])
+    finally:
+        kernels._lib.tc_status_word(torch.device("cuda:0")).zero_()
+        kernels.check_tc_status()
+        eng.release(s)

@@ -50,6 +50,7 @@ class Engine:
         self.steps_run = 0
         self.use_graphs = model.graph_capturable      # replay captured CUDA graphs for decode steps
         self._decode_graphs: dict[int, "DecodeGraph"] = {}
+        self._replays_unchecked = 0                   # replayed decode steps since the kernels' status word was read
         self.h2d_bytes = 0            # bytes of step inputs copied to the device so far
 
     # ---- construction -------------------------------------------------------
@@ -165,6 +166,11 @@ class Engine:
                                                                          len(rows))
                 logits = graph.run(rows)
                 self.h2d_bytes += graph.batch.packed_bytes
+                self._replays_unchecked += 1
+                if self._replays_unchecked >= 256:      # the check waits for the device: now and then is enough
+                    self._replays_unchecked = 0
+                    kernels.mark_tc_launched()
+                    kernels.check_tc_status()
             else:
                 batch = build_step_batch(rows, self.cache, self.runtime.device)
                 logits = self.model.forward(batch, self.cache)

@@ -69,6 +69,11 @@ def tc_status_word(device) -> torch.Tensor:
     return t
 
 
+def mark_tc_launched() -> None:
+    """Replayed graphs launch tcgen05 kernels without passing through tc_status_word(): the caller says so."""
+    _tc_launched[0] += 1
+
+
 def check_tc_status() -> None:
     """Raises if a tcgen05 kernel launched since the last check gave up on a
     pipeline wait (its output is then invalid).  Synchronises with the device."""
