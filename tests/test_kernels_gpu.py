@@ -460,6 +460,39 @@ def test_tcgen05_prompt_attention_under_load_agrees_with_the_mma_kernel(monkeypa
         assert float(excess.max()) <= 0, f"run {rep}: {float((got - want).abs().max()):.3e}"
 
 
+@pytest.mark.parametrize("window", [1000, 64, 129])
+def test_tcgen05_prompt_attention_with_a_window_over_long_prompts(window, monkeypatch):
+    """A window far shorter than the prompt: most key tiles of a block lie outside its range and are never
+    loaded, the first and last tiles of the range are cut by the window's edge and by the diagonal."""
+    from tq_kv_b200 import kernels
+    import importlib
+    att = importlib.import_module("tq_kv_b200.kernels.attention")
+    nh, nkv, hd, lens = 8, 2, 128, [4096, 3001]
+    T = sum(lens)
+    cu = torch.tensor([0, 4096, T], dtype=torch.int32, device=DEV)
+    tok_seq = torch.cat([torch.zeros(4096), torch.ones(3001)]).int().to(DEV)
+    tok_pos = torch.cat([torch.arange(4096), torch.arange(3001)]).int().to(DEV)
+    start = torch.zeros(2, dtype=torch.int32, device=DEV)
+    q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=1, scale=2.0)
+    k, v = rnd(T, nkv * hd, dtype=torch.bfloat16, seed=2), rnd(T, nkv * hd, dtype=torch.bfloat16, seed=3)
+    outs = []
+    for tc in (False, True):
+        monkeypatch.setattr(att, "USE_TC_ATTENTION", tc)
+        out = torch.empty_like(q)
+        kernels.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd, tok_pos=tok_pos, tok_seq=tok_seq,
+                          cu_seqlens=cu, start_pos=start, window=window, k_packed=k, v_packed=v)
+        outs.append(out.float())
+    kernels.check_tc_status()
+    # the mma.sync kernel against the plain attention on a few rows of each prompt, then the two kernels on all
+    for b, n in enumerate(lens):
+        a = int(cu[b])
+        rows = [0, 63, 64, window - 1, window, window + 1, n // 2, n - 1]
+        want = plain_attention(q[a:a + n].cpu()[rows], k[a:a + n].cpu(), v[a:a + n].cpu(), nh, nkv, hd, window, rows)
+        close(outs[0][a:a + n][rows], want, 1.6e-2, f"mma, prompt {b}")
+    excess = (outs[1] - outs[0]).abs() - (8e-3 + 2.0 ** -6 * outs[0].abs())
+    assert float(excess.max()) <= 0, f"{float((outs[1] - outs[0]).abs().max()):.3e}"
+
+
 def _paged(k, v, nkv, hd, table_row, P=64):
     """Scatters [Tk, nkv*hd] keys/values into pages per `table_row`."""
     n_pages = max(table_row) + 2
