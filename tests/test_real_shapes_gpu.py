@@ -147,3 +147,25 @@ def test_deterministic_switch_gives_the_same_bits_twice(tmp_path):
         results.append(torch.load(out))
     assert torch.isfinite(results[0]).all()
     assert torch.equal(results[0], results[1])
+
+
+@pytest.mark.parametrize("shape", ["qwen2.5-7b", "qwen2.5-0.5b"])
+def test_a_long_prompt_whole_and_in_chunks_agree(shape):
+    """1,500 tokens in one step (attention over the step's packed keys) and as 700 + 800 (the second chunk reads
+    the first from the paged cache through TMA): the logits at the chunk's positions must agree."""
+    import tq_kv_b200 as tq
+    from tq_kv_b200.engine import Engine, StepRow
+    cfg = dict(tq.named_shape(shape))
+    cfg.update(num_hidden_layers=2, max_window_layers=2, vocab_size=VOCAB)
+    eng = Engine.from_random(cfg, seed=2, dtype="bfloat16", max_slots=2, max_context=2048)
+    toks = random_tokens(1500, VOCAB, 41)
+    want_rows = [700, 701, 1023, 1024, 1499]
+    s = eng.new_sequence()
+    whole = eng.step([StepRow(s, toks, want_rows)]).float().cpu()
+    eng.release(s)
+    s = eng.new_sequence()
+    eng.step([StepRow(s, toks[:700], [])])
+    chunked = eng.step([StepRow(s, toks[700:], [r - 700 for r in want_rows])]).float().cpu()
+    eng.release(s)
+    assert torch.isfinite(whole).all() and torch.isfinite(chunked).all()
+    assert float((whole - chunked).abs().max()) <= 0.03 * max(1.0, float(whole.abs().max()))
