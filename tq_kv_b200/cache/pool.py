@@ -89,7 +89,12 @@ class GroupPages:
         return n if self.ring_pages is None else min(n, self.ring_pages)
 
     def need(self, slot: int, new_length: int) -> int:
-        return max(0, self.pages_for_length(new_length) - len(self.pages.get(slot, ())))
+        n = -(-new_length // self.page_tokens)
+        if self.ring_pages is not None and n > self.ring_pages:
+            n = self.ring_pages
+        have = self.pages.get(slot)
+        n -= len(have) if have is not None else 0
+        return n if n > 0 else 0
 
     def grow(self, slot: int, new_length: int) -> None:
         have = self.pages.setdefault(slot, [])
@@ -134,15 +139,25 @@ class SlotBook:
             if self.length[s] + n > self.max_length:
                 raise CacheError(
                     f"slot {s}: {self.length[s]} cached + {n} new tokens exceed the context limit {self.max_length}")
+        # pages each row needs in each group, counted once (a decode step of many rows passes here every token)
+        new_lengths = [self.length[s] + n for s, n in zip(slots, new_tokens)]
+        needs = []
         for g in self.groups:
-            want = sum(g.need(s, self.length[s] + n) for s, n in zip(slots, new_tokens))
+            row = [g.need(s, length) for s, length in zip(slots, new_lengths)]
+            want = sum(row)
             if want > g.pool.free_count:
                 raise CacheError(
                     f"cache group '{g.name}' is full: the step needs {want} more pages of {g.page_tokens} tokens, "
                     f"{g.pool.free_count} of {g.pool.n} are free")
-        for g in self.groups:
-            for s, n in zip(slots, new_tokens):
-                g.grow(s, self.length[s] + n)
+            needs.append(row if want else None)
+        for g, row in zip(self.groups, needs):
+            if row is None:
+                continue
+            for s, k in zip(slots, row):
+                if k:
+                    have = g.pages.setdefault(s, [])
+                    for _ in range(k):
+                        have.append(g.pool.take())
 
     def commit(self, slots: list[int], new_tokens: list[int]) -> None:
         for s, n in zip(slots, new_tokens):

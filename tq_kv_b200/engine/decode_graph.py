@@ -63,6 +63,8 @@ class DecodeGraph:
         self.graph = None
         self.logits = None
         self.kernels_per_replay = 0
+        self._tables = [np.zeros((B, w), dtype=np.int32) for w in self.widths]      # see _fill
+        self._seen = [[(None, -1)] * B for _ in self.widths]
 
     def _fill(self, rows) -> torch.Tensor:
         i = self.turn % self.RING
@@ -79,11 +81,18 @@ class DecodeGraph:
         a[o[4]:o[4] + B] = slots
         a[o[5]:o[5] + B] = starts
         a[o[6]:o[6] + B] = [s + 1 for s in starts]
+        # Block tables: a row changes only when its sequence gets a page or the slot gets another sequence, so
+        # the rows are kept on the host and only those whose page list (the object or its length) is another
+        # than last time are rewritten; the whole table then goes into the staging buffer in one copy.
         for gi, w in enumerate(self.widths):
             trows, _ = cache.block_table_rows(gi, slots)
-            base = o[8 + gi]
+            table, seen = self._tables[gi], self._seen[gi]
             for b, pages in enumerate(trows):
-                a[base + b * w: base + b * w + len(pages)] = pages
+                last = seen[b]
+                if last[0] is not pages or last[1] != len(pages):
+                    table[b, :len(pages)] = pages
+                    seen[b] = (pages, len(pages))
+            a[o[8 + gi]:o[8 + gi] + B * w] = table.reshape(-1)
         self.batch.host_slots = slots
         self.dev.copy_(h, non_blocking=True)
         ev = torch.cuda.Event()
