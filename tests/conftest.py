@@ -23,3 +23,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The largest logit errors (relative to the largest logit) that assert_close saw, by precision."""
+    try:
+        import helpers
+    except Exception:
+        return
+    for dtype, (ratio, what) in sorted(helpers.worst.items()):
+        terminalreporter.write_line(f"largest logit error seen, {dtype}: {ratio:.3e} of max |logit| ({what}); "
+                                    f"bound {helpers.TOL[dtype]:.1e}")

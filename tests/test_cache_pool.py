@@ -126,3 +126,36 @@ def test_sequence_cache_groups_and_state():
     s2 = c.alloc_slot()
     assert s2 == s and float(c.state[3][s2].abs().sum()) == 0.0          # state is zeroed when a slot is handed out
     assert c.length(s2) == 0 and c.free_pages() == 10
+
+
+def test_trim_gives_back_pages_reserved_for_a_step_that_did_not_happen():
+    b = _book(slots=2, pages=8, ring=2)
+    s = b.alloc()
+    b.reserve([s], [70])
+    b.commit([s], [70])
+    before = {g.name: list(g.pages[s]) for g in b.groups}
+    b.reserve([s], [200])                       # the step then fails: nothing is committed
+    held = b.groups[0].pages[s]
+    assert len(held) == 5
+    b.trim([s])
+    assert {g.name: g.pages[s] for g in b.groups} == before
+    assert b.groups[0].pages[s] is not held     # a new list, so that cached views of the old one are seen stale
+    assert b.groups[0].pool.free_count == 6
+    b.check()
+    b.trim([s])                                 # nothing to give back: no change
+    b.check()
+    b.free(s)
+    assert b.groups[0].pool.free_count == 8 and b.groups[1].pool.free_count == 8
+
+
+def test_ring_holds_the_window_plus_the_slack():
+    from tq_kv_b200.cache import ring_pages_for
+    assert ring_pages_for(16, 0) == 1 and ring_pages_for(64, 0) == 1 and ring_pages_for(65, 0) == 2
+    assert ring_pages_for(64, 63) == 2 and ring_pages_for(128, 63) == 3 and ring_pages_for(16, 63) == 2
+    for window in (8, 16, 64, 70, 128, 4096):
+        for chunk in (1, 17, 64, 200):
+            ring_tokens = ring_pages_for(window, chunk - 1) * PAGE_TOKENS
+            assert ring_tokens - window + 1 >= chunk            # a step of `chunk` tokens always fits
+    c = SequenceCache({0: KVRequest(1, 16, 64)}, {}, max_tokens=1024, max_slots=2, max_length=1024,
+                      dtype=torch.float32, device="cpu", window_slack=63)
+    assert c.groups[0].ring_pages == 2

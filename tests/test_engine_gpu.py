@@ -197,8 +197,8 @@ def test_refused_steps_change_nothing(tmp_root):
         eng.step([StepRow(s, [1] * 150, [])])
     eng.release(other)
     eng.step([StepRow(s, [1, 2, 3], [])])
-    with pytest.raises(KernelError, match="window"):                    # 60 tokens onto a 64-key ring with window 16
-        eng.step([StepRow(s, [1] * 60, [])])
+    with pytest.raises(KernelError, match="window"):                    # 120 tokens onto a 128-key ring, window 16
+        eng.step([StepRow(s, [1] * 120, [])])
     assert eng.length(s) == 3
     with pytest.raises(StepError, match="not held"):
         eng.step([StepRow(5, [1], [])])
@@ -321,21 +321,43 @@ def test_an_entry_can_read_another_entrys_cache(tmp_root):
         unregister_architecture("SharedForCausalLM")
 
 
-def test_replayed_steps_read_the_kernels_status_word_now_and_then(tmp_root):
-    """Replayed decode steps do not wait for the device, so the status word of the tcgen05 kernels is read only
-    every 256 of them; a bit raised in between must still surface as an error (here raised by hand)."""
+def test_a_wait_that_ran_out_in_a_replayed_step_surfaces_in_short_runs(tmp_root):
+    """Replayed decode steps do not wait for the device.  A bit raised in the status word of the tcgen05
+    kernels (here by hand) must still stop a short generation, and `check_status()` must report it to
+    whoever replays steps himself; afterwards the word is clear again."""
+    import tq_kv_b200 as tq
     from tq_kv_b200 import kernels
     from tq_kv_b200.engine import StepRow
     eng, _ = engine_for(tmp_root, "b", "bfloat16")
+    word = kernels._lib.report_buffer(torch.device("cuda:0"))[:1]
     s = eng.new_sequence()
-    eng.step([StepRow(s, [1, 2, 3], [])])
-    eng.step([StepRow(s, [4], [0])])                       # a replayed step
-    eng._replays_unchecked = 255
-    kernels._lib.tc_status_word(torch.device("cuda:0")).fill_(2)
     try:
+        eng.step([StepRow(s, [1, 2, 3], [])])
+        eng.step([StepRow(s, [4], [0])])                       # a replayed step
+        word.fill_(2)
+        eng.step([StepRow(s, [5], [0])])                       # replays do not look
         with pytest.raises(kernels.KernelError, match="wait ran out"):
-            eng.step([StepRow(s, [5], [0])])
-    finally:
-        kernels._lib.tc_status_word(torch.device("cuda:0")).zero_()
-        kernels.check_tc_status()
+            eng.check_status()
+        eng.check_status()                                     # cleared
         eng.release(s)
+        s = None
+        # a generation of four tokens: the loop reads the word with every step's ids
+        real_step, calls = eng.step, []
+
+        def step_then_raise_the_bit(rows, **kw):
+            out = real_step(rows, **kw)
+            calls.append(1)
+            if len(calls) == 2:
+                word.fill_(2)
+            return out
+
+        eng.step = step_then_raise_the_bit
+        with pytest.raises(kernels.KernelError, match="wait ran out"):
+            eng.generate([[1, 2, 3]], tq.GenerationParams.greedy(4, stop_token_ids=()))
+        assert eng.cache.free_slots == eng.cache.max_slots     # the failed batch gave its slot back
+    finally:
+        eng.__dict__.pop("step", None)
+        word.zero_()
+        kernels.check_tc_status()
+        if s is not None:
+            eng.release(s)

@@ -169,3 +169,88 @@ def test_uniform_depends_on_seed_request_and_index_only():
     assert len({uniform(1, r, i) for r in range(10) for i in range(10)}) == 100
     assert uniform(2, 2, 3) != a
     assert float(torch.tensor(a, dtype=torch.float32)) == a
+
+
+# ---- the loop that runs one step ahead of the tokens it has read ---------------------------------------------
+class FakeSampledIds:
+    """Stand-in for the device buffer of sampled ids: `fetch` snapshots it, `wait` hands the snapshot over."""
+
+    def __init__(self):
+        self.ids = torch.zeros(64, dtype=torch.int32)
+        self.rows, self.d2h_bytes = 64, 0
+
+    def fetch(self, n):
+        return self.ids[:n].clone()
+
+    def wait(self, ticket):
+        return ticket.tolist()
+
+
+class AheadEngine(FakeEngine):
+    """A scripted engine whose rows may take their token from the sampled ids."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.sampled = FakeSampledIds()
+        self.sources = []
+
+    def step(self, rows, keep_logits=True):
+        from tq_kv_b200.engine import StepRow
+        self.sources.append([r.source for r in rows])
+        real = [StepRow(r.slot, [int(self.sampled.ids[r.source])] if r.source is not None else r.tokens, r.want)
+                for r in rows]
+        return super().step(real)
+
+
+class DeviceArgmaxSampler(ArgmaxSampler):
+    def sample_device(self, logits, requests, index, out=None):
+        assert logits.shape[0] == self.n_rows == len(requests)
+        out[:logits.shape[0]] = logits.argmax(-1).to(torch.int32)
+        return out
+
+
+def _both(prompts, slots, **kw):
+    outs = []
+    for pipeline in (False, True):
+        e = AheadEngine(slots=slots)
+        params = GenerationParams.greedy(kw.get("max_tokens", 4))
+        if "stop_token_ids" in kw:
+            params.stop_token_ids = kw["stop_token_ids"]
+        seen = []
+        res = generate(e, prompts, params, sampler_factory=DeviceArgmaxSampler, pipeline=pipeline,
+                       on_token=lambda i, t: seen.append((i, t)))
+        assert not e.held and e.cache.free_slots == slots
+        outs.append((e, res, seen))
+    return outs
+
+
+def test_running_ahead_gives_the_same_tokens_reasons_and_callbacks():
+    for prompts, kw in (([[5], [1], [3, 4, 5]], dict(max_tokens=6)),             # stop id 7 found late, twice
+                        ([[6]], dict(max_tokens=5)),                            # the first sampled token stops
+                        ([[1], [2], [3], [4], [8]], dict(max_tokens=2, stop_token_ids=())),
+                        ([[5], [5]], dict(max_tokens=5))):                       # all rows stop in the same round
+        (e0, r0, s0), (e1, r1, s1) = _both(prompts, slots=3, **kw)
+        assert [r.tokens for r in r0] == [r.tokens for r in r1]
+        assert [r.finish_reason for r in r0] == [r.finish_reason for r in r1]
+        assert s0 == s1
+        assert e0.alloc_log == e1.alloc_log
+
+
+def test_running_ahead_never_steps_past_a_length_or_context_end():
+    (e0, _, _), (e1, _, _) = _both([[1], [10, 11], [3, 4, 5]], slots=3, max_tokens=3, stop_token_ids=())
+    assert [len(s) for s in e1.steps] == [len(s) for s in e0.steps] == [3, 3, 3]
+    assert e1.sources[1:] == [[0, 1, 2], [0, 1, 2]]                  # decode rows are fed on the device
+    e = AheadEngine(max_context=4)
+    params = GenerationParams.greedy(10)
+    params.stop_token_ids = ()
+    res = generate(e, [[1, 2]], params, sampler_factory=DeviceArgmaxSampler)
+    assert res[0].tokens == [3, 4, 5] and res[0].finish_reason == "context"
+    assert sum(len(r[1]) for s in e.steps for r in s) == 4
+
+
+def test_a_stop_found_late_costs_one_row_of_one_step():
+    (e0, r0, _), (e1, r1, _) = _both([[5], [1]], slots=2, max_tokens=5)
+    assert r1[0].tokens == [6] and r1[0].finish_reason == "stop"
+    assert [len(s) for s in e0.steps] == [2, 2, 1, 1, 1]
+    assert [len(s) for s in e1.steps] == [2, 2, 2, 1, 1]             # request 0 rides along once more
+    assert e1.sources[3] == [1]                                      # then row 1 of the last ids feeds the only row

@@ -99,3 +99,29 @@ def test_golden_values(tmp_path):
         got = logits[g["positions"]][:, g["columns"]]
         assert torch.allclose(got, torch.tensor(g["logits"]), atol=2e-6), name
         assert [int(x) for x in logits.argmax(-1)] == g["argmax"]
+
+
+def test_the_planted_key_decides_the_logits(tmp_path):
+    """A check of the tests that use helpers.planted_model(): in the plain
+    implementation, a window one key wider or narrower moves the logits at
+    the query's two places by the size of the logits themselves, and so does
+    taking the far key away; rounding to bfloat16 moves them a hundred times
+    less.  An engine that is off by one key therefore cannot pass there."""
+    from helpers import TINY_C, TOL, planted_model, planted_tokens
+    folder = planted_model(tmp_path, "float32", windowed=True)
+    cfg, w = pm.read_model_folder(folder)
+    T, W = 150, TINY_C["sliding_window"]
+    toks = planted_tokens(T + 1, T - W, [T - 1, T], 5)
+    want = pm.decoder_logits(cfg, w, toks)
+    scale = float(want.abs().max())
+    wider = pm.decoder_logits({**cfg, "sliding_window": W + 1}, w, toks)
+    narrower = pm.decoder_logits({**cfg, "sliding_window": W - 1}, w, toks)
+    assert float((wider - want)[T].abs().max()) > 0.5 * scale > 10 * TOL["bfloat16"] * scale
+    assert float((narrower - want)[T - 1].abs().max()) > 0.5 * scale
+    folder = planted_model(tmp_path, "float32", windowed=False)
+    cfg, w = pm.read_model_folder(folder)
+    toks = planted_tokens(300, 2, [299], 6)
+    want = pm.decoder_logits(cfg, w, toks)
+    gone = list(toks)
+    gone[2] = 3
+    assert float((pm.decoder_logits(cfg, w, gone) - want)[299].abs().max()) > 0.3 * float(want.abs().max())

@@ -18,7 +18,7 @@ from helpers import TINY_A, assert_close, random_tokens
 pytestmark = pytest.mark.gpu
 
 
-def _register():
+def _register(capturable=False):
     from dataclasses import replace
 
     from tq_kv_b200.cache import StateRequest
@@ -27,7 +27,7 @@ def _register():
     from tq_kv_b200.parts import Mixer, WeightSpec, register_part
 
     class RunningMeanMixer(Mixer):
-        graph_capturable = False          # its step reads the batch's layout back to the host
+        graph_capturable = capturable     # False: every step reads the batch's layout back to the host
 
         def __init__(self, spec):
             super().__init__(spec)
@@ -47,6 +47,12 @@ def _register():
         def forward(self, x, ctx, residual):
             b = ctx.batch
             u = x.float() @ self.w_in.T
+            if capturable and b.single_tokens:
+                # one token per row: everything stays on the device, so the step can be captured and replayed
+                slots = b.slots.long()
+                ctx.state.index_add_(0, slots, u)
+                residual += (ctx.state[slots] / (b.tok_pos + 1).unsqueeze(1)) @ self.w_out.T
+                return
             cu = b.cu_seqlens.tolist()
             for row, slot in enumerate(b.host_slots):
                 a, e = cu[row], cu[row + 1]
@@ -126,6 +132,50 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         s = eng.new_sequence()                                      # reused slot: its state starts from zero again
         assert_close(eng.step([StepRow(s, reqs[2], [8])]), wants[2][8:9], "float32", "reused slot")
         eng.release(s)
+    finally:
+        unregister_architecture("ToyMixForCausalLM")
+        unregister_part("toy_running_mean")
+
+
+def test_a_stateful_mixer_in_replayed_graphs_advances_its_state_once_per_step(tmp_path):
+    """Decode steps of a model whose mixer keeps state are captured and
+    replayed; the first step of every batch size runs once, not twice, so the
+    logits equal those of plain launches and of the plain implementation."""
+    from tq_kv_b200.config import unregister_architecture
+    from tq_kv_b200.engine import Engine, StepRow
+    from tq_kv_b200.parts import unregister_part
+    from tq_kv_b200.weights import write_model_folder
+    _register(capturable=True)
+    try:
+        cfg = {**TINY_A, "architectures": ["ToyMixForCausalLM"], "num_hidden_layers": 3, "max_window_layers": 3}
+        folder = write_model_folder(cfg, str(tmp_path / "toy"), seed=5)
+        c, w = pm.read_model_folder(folder)
+        reqs = [random_tokens(n, 256, 70 + n) for n in (30, 12, 20)]
+        wants = [_plain(c, w, t) for t in reqs]
+        outs = {}
+        for graphs in (True, False):
+            eng = Engine.from_folder(folder, dtype="float32", max_tokens=512, max_slots=3)
+            assert eng.use_graphs                       # the toy part declares itself capturable
+            eng.use_graphs = graphs
+            slots = [eng.new_sequence() for _ in reqs]
+            cut = [6, 4, 5]
+            eng.step([StepRow(s, t[:c_], []) for s, t, c_ in zip(slots, reqs, cut)])
+            got, live = [], [0, 1, 2]
+            while live:                                 # batch sizes 3, 2, 1: three first uses of a graph
+                out = eng.step([StepRow(slots[i], [reqs[i][cut[i]]], [0]) for i in live])
+                assert_close(out, torch.stack([wants[i][cut[i]] for i in live]), "float32",
+                             f"graphs={graphs}, decode at {[cut[i] for i in live]}")
+                got.append(out.clone())
+                for i in list(live):
+                    cut[i] += 1
+                    if cut[i] == len(reqs[i]):
+                        eng.release(slots[i])
+                        live.remove(i)
+            outs[graphs] = torch.cat(got)
+            if graphs:
+                assert sorted(eng._decode_graphs) == [1, 2, 3]
+        # the two differ by rounding only: a graph plans attention's splits for the context limit
+        assert_close(outs[True], outs[False].cpu(), "float32", "graph vs plain launches")
     finally:
         unregister_architecture("ToyMixForCausalLM")
         unregister_part("toy_running_mean")

@@ -122,3 +122,28 @@ def test_file_errors(tmp_path):
     (tmp_path / "bad.safetensors").write_bytes(b"\xff" * 4)
     with pytest.raises(SafetensorsError):
         load_tensors(str(tmp_path), {}, [], mode=torch.float32, device="cpu")
+
+
+def test_random_weights_depend_on_seed_name_and_element_only():
+    from tq_kv_b200.weights.random_init import random_tensor, standard_normal_host, tensor_key
+    a = random_tensor("x.weight", (7, 9), "matrix", 3, torch.float32, "cpu")
+    assert torch.equal(a, random_tensor("x.weight", (7, 9), "matrix", 3, torch.float32, "cpu"))
+    assert torch.equal(a.flatten()[:20], random_tensor("x.weight", (20,), "matrix", 3, torch.float32, "cpu"))
+    assert not torch.equal(a, random_tensor("y.weight", (7, 9), "matrix", 3, torch.float32, "cpu"))
+    assert not torch.equal(a, random_tensor("x.weight", (7, 9), "matrix", 4, torch.float32, "cpu"))
+    key = tensor_key(3, "x.weight")
+    whole = standard_normal_host(key, 0, 5000)
+    assert (standard_normal_host(key, 1234, 100) == whole[1234:1334]).all()       # any range, any chunking
+    b = random_tensor("x.weight", (7, 9), "matrix", 3, torch.bfloat16, "cpu")
+    assert torch.equal(b, a.to(torch.bfloat16))                                    # rounded once, from float32
+
+
+def test_random_weights_are_normal_with_the_roles_moments():
+    from tq_kv_b200.weights.random_init import random_tensor
+    m = random_tensor("m", (400, 500), "matrix", 1, torch.float32, "cpu").double()
+    assert abs(float(m.mean())) < 2e-4 and abs(float(m.std()) - 0.02) < 2e-4
+    z = m / 0.02
+    assert abs(float((z ** 3).mean())) < 0.03 and abs(float((z ** 4).mean()) - 3.0) < 0.06
+    assert float(z.abs().max()) < 5.8 and torch.isfinite(m).all()
+    n = random_tensor("n", (4096,), "norm_scale", 1, torch.float32, "cpu").double()
+    assert abs(float(n.mean()) - 1.0) < 6e-3 and abs(float(n.std()) - 0.1) < 6e-3

@@ -19,11 +19,14 @@ from .engine import Engine
 
 
 def load(model: str, *, dtype: str = "bfloat16", device: str = "cuda:0", random_weights: bool = False, seed: int = 0,
-         max_batch: int = 8, max_context: Optional[int] = None, max_tokens: Optional[int] = None) -> Engine:
+         max_batch: int = 8, max_context: Optional[int] = None, max_tokens: Optional[int] = None,
+         window_chunk: int = 64) -> Engine:
     """An engine for `model`: a folder with config.json and safetensors files,
     or — with `random_weights` — a folder's config.json or the name of a shape
     (`tq_kv_b200.shape_names()`).  The cache holds `max_batch` sequences of
-    `max_context` tokens unless `max_tokens` (tokens held together) is given."""
+    `max_context` tokens unless `max_tokens` (tokens held together) is given.
+    `window_chunk` is the most tokens one step may add to a sequence it
+    continues in a layer with a sliding window."""
     if random_weights:
         if os.path.isdir(model) or os.path.isfile(model):
             from .config import read_config_json
@@ -31,12 +34,12 @@ def load(model: str, *, dtype: str = "bfloat16", device: str = "cuda:0", random_
         else:
             cfg = named_shape(model)
         return Engine.from_random(cfg, seed, dtype=dtype, device=device, max_tokens=max_tokens, max_slots=max_batch,
-                                  max_context=max_context)
+                                  max_context=max_context, window_chunk=window_chunk)
     if not os.path.isdir(model):
         hint = f" ('{model}' is a shape name: pass random_weights=True)" if model in shape_names() else ""
         raise FileNotFoundError(f"model folder '{model}' does not exist{hint}")
     return Engine.from_folder(model, dtype=dtype, device=device, max_tokens=max_tokens, max_slots=max_batch,
-                              max_context=max_context)
+                              max_context=max_context, window_chunk=window_chunk)
 
 
 class EngineBuilder:

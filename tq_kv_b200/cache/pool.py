@@ -163,6 +163,22 @@ class SlotBook:
         for s, n in zip(slots, new_tokens):
             self.length[s] += n
 
+    def trim(self, slots: list[int]) -> None:
+        """Gives back the pages of `slots` beyond what their committed lengths
+        need (pages reserved for a step that did not happen)."""
+        for s in slots:
+            if not self.slots.is_held(s):
+                continue
+            for g in self.groups:
+                have = g.pages.get(s)
+                if have is None:
+                    continue
+                keep = g.pages_for_length(self.length[s])
+                if len(have) > keep:
+                    for p in have[keep:]:
+                        g.pool.give_back(p)
+                    g.pages[s] = have[:keep]       # a new list: whoever remembers the old one sees the change
+
     def check(self) -> None:
         self.slots.check()
         for g in self.groups:

@@ -52,14 +52,24 @@ class KVLayerView:
     writes: bool                     # False: the layer reads another layer's cache
 
 
+def ring_pages_for(window: int, slack: int) -> int:
+    """Pages a sequence keeps in a window group.  A step that continues a
+    sequence by n tokens writes all n keys before any of its queries reads, so
+    the first query still finds its oldest key only if window + n - 1 keys fit:
+    the ring holds `slack` keys more than the window (n <= slack + 1 always
+    fits), rounded up to whole pages."""
+    return -(-(window + max(0, slack)) // PAGE_TOKENS)
+
+
 class KVGroup:
-    def __init__(self, name: str, request: KVRequest, entries: list[int], n_pages: int, dtype, device):
+    def __init__(self, name: str, request: KVRequest, entries: list[int], n_pages: int, dtype, device,
+                 window_slack: int = 0):
         self.name = name
         self.request = request
         self.entries = list(entries)
         ring = None
         if request.window is not None:
-            ring = -(-request.window // PAGE_TOKENS)
+            ring = ring_pages_for(request.window, window_slack)
         self.book = GroupPages(name, n_pages, PAGE_TOKENS, ring)
         shape = (len(entries), n_pages, request.n_kv_heads, PAGE_TOKENS, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
@@ -82,7 +92,8 @@ class SequenceCache:
     (each sequence rounded up to whole pages)."""
 
     def __init__(self, kv_requests: dict[int, KVRequest], state_requests: dict[int, StateRequest], *,
-                 max_tokens: int, max_slots: int, max_length: int, dtype: torch.dtype, device):
+                 max_tokens: int, max_slots: int, max_length: int, dtype: torch.dtype, device,
+                 window_slack: int = 0):
         if max_tokens <= 0 or max_slots <= 0 or max_length <= 0:
             raise CacheError("cache sizes must be positive")
         self.device = torch.device(device)
@@ -98,10 +109,10 @@ class SequenceCache:
             if req.window is None:
                 n_pages, name = total_pages, f"all-keys/{req.n_kv_heads}x{req.head_dim}"
             else:
-                ring = -(-req.window // PAGE_TOKENS)
+                ring = ring_pages_for(req.window, window_slack)
                 n_pages = min(total_pages, max_slots * ring)
                 name = f"window-{req.window}/{req.n_kv_heads}x{req.head_dim}"
-            g = KVGroup(name, req, entries, n_pages, dtype, self.device)
+            g = KVGroup(name, req, entries, n_pages, dtype, self.device, window_slack)
             self.groups.append(g)
             for li, entry in enumerate(entries):
                 self.group_of_entry[entry] = (gi, li)
@@ -134,6 +145,9 @@ class SequenceCache:
 
     def commit(self, slots: list[int], new_tokens: list[int]) -> None:
         self.book.commit(slots, new_tokens)
+
+    def trim(self, slots: list[int]) -> None:
+        self.book.trim(slots)
 
     def block_table_rows(self, group: int, slots: list[int]) -> tuple[list[list[int]], int]:
         """The page lists of `slots` in group `group` and the widest of them."""

@@ -26,7 +26,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 GROUPS: dict[str, list[str]] = {
     # everything a model needs in either precision
     "core": ["elementwise.cu", "attention.cu", "flash_decode.cu", "flash_prefill.cu", "flash_prefill_tc.cu", "gemm.cu", "skinny_gemm.cu",
-             "gemm_tc.cu", "decode_gemm_tc.cu", "sampling.cu"],
+             "gemm_tc.cu", "decode_gemm_tc.cu", "sampling.cu", "random_fill.cu"],
     # decode attention for callers that cannot allocate: a library of its own (flash_decode_static.h)
     "noalloc": ["flash_decode_static.cu"],
 }

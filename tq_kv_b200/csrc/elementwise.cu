@@ -416,3 +416,27 @@ TQ_API int tq_add_into(float* acc, const void* x, int in_dtype, size_t total, cu
     else return (int)cudaErrorInvalidValue;
     return tq_launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// tokens[i] = sampled[src[i]] where src[i] >= 0: the next token of a sequence
+// taken from the sampler's output on the device (row src[i] of the ids it
+// wrote last), so that decode steps can follow one another without the host
+// reading a token back in between.  Entries with src[i] < 0 keep the id the
+// host put there.
+// ---------------------------------------------------------------------------
+__global__ void select_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
+                                     const int* __restrict__ sampled, int n) {
+    pdl_wait();
+    pdl_launch();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const int s = src[i];
+        if (s >= 0) tokens[i] = sampled[s];
+    }
+}
+
+TQ_API int tq_select_tokens(int* tokens, const int* src, const int* sampled, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, select_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens,
+                         src, sampled, n);
+}

@@ -3,6 +3,7 @@ in a single copy."""
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import Optional
 
 import numpy as np
 import torch
@@ -14,10 +15,13 @@ from ..parts import StepBatch
 @dataclass
 class StepRow:
     """One sequence's share of a step: its cache slot, the tokens it brings
-    and the places among them whose logits are wanted."""
+    and the places among them whose logits are wanted.  A row of one token
+    may name `source` instead of the token's value: the row of the ids the
+    sampler wrote last (on the device) that holds it; `tokens` is then [0]."""
     slot: int
     tokens: list[int]
     want: list[int]
+    source: Optional[int] = None
 
 
 def _pad4(n: int) -> int:
@@ -27,8 +31,8 @@ def _pad4(n: int) -> int:
 def build_step_batch(rows: list[StepRow], cache: SequenceCache, device) -> StepBatch:
     """Packs `rows` (already reserved in the cache).  Layout of the buffer:
     tokens | tok_seq | tok_pos | cu_seqlens | slots | start_pos | new_lens |
-    logit_rows | one block table per cache group; every segment starts on a
-    16-byte boundary."""
+    logit_rows | tok_src | one block table per cache group; every segment
+    starts on a 16-byte boundary."""
     B = len(rows)
     lens = [len(r.tokens) for r in rows]
     T = sum(lens)
@@ -37,7 +41,7 @@ def build_step_batch(rows: list[StepRow], cache: SequenceCache, device) -> StepB
     R = sum(len(r.want) for r in rows)
     tables = [cache.block_table_rows(gi, slots) for gi in range(len(cache.groups))]
 
-    seg_sizes = [T, T, T, B + 1, B, B, B, R] + [B * max(w, 1) for _, w in tables]
+    seg_sizes = [T, T, T, B + 1, B, B, B, R, T] + [B * max(w, 1) for _, w in tables]
     offs, total = [], 0
     for s in seg_sizes:
         offs.append(total)
@@ -60,9 +64,13 @@ def build_step_batch(rows: list[StepRow], cache: SequenceCache, device) -> StepB
         for w in r.want:
             buf[o] = int(cu[b]) + w
             o += 1
+    buf[offs[8]: offs[8] + T] = -1
+    for b, r in enumerate(rows):
+        if r.source is not None:
+            buf[offs[8] + int(cu[b])] = r.source
     for gi, (trows, width) in enumerate(tables):
         w = max(width, 1)
-        base = offs[8 + gi]
+        base = offs[9 + gi]
         for b, pages in enumerate(trows):
             buf[base + b * w: base + b * w + len(pages)] = pages
 
@@ -78,5 +86,6 @@ def build_step_batch(rows: list[StepRow], cache: SequenceCache, device) -> StepB
     return StepBatch(
         n_tokens=T, n_seqs=B, tokens=seg(0, T), tok_seq=seg(1, T), tok_pos=seg(2, T), cu_seqlens=seg(3, B + 1),
         slots=seg(4, B), start_pos=seg(5, B), new_lens=seg(6, B), logit_rows=seg(7, R), n_logit_rows=R,
-        block_tables=[(seg(8 + gi, B * max(w, 1)), max(w, 1)) for gi, (_, w) in enumerate(tables)],
-        host_slots=slots, host_start=starts, host_lens=lens, packed_bytes=int(buf.nbytes))
+        block_tables=[(seg(9 + gi, B * max(w, 1)), max(w, 1)) for gi, (_, w) in enumerate(tables)],
+        host_slots=slots, host_start=starts, host_lens=lens, packed_bytes=int(buf.nbytes), tok_src=seg(8, T),
+        any_source=any(r.source is not None for r in rows))

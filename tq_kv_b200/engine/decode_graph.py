@@ -6,13 +6,19 @@ is therefore captured once into a CUDA graph over static buffers (the packed
 step metadata with block tables of full width, the logits) and replayed:
 per step, the host fills one pinned staging buffer, copies it to the device
 and replays.  Staging buffers form a small ring, each guarded by an event, so
-that the host may run a few steps ahead of the device.
+that the host may run a few steps ahead of the device.  A row's token is
+either in the staging buffer or, if the row names a `source`, taken on the
+device from the ids the sampler wrote last (the captured step begins with
+that selection), so that the host can launch a step before it has read the
+token that feeds it.
 
 The captured step is the same `DecoderModel.forward` that an uncaptured step
 runs; only planning inputs are frozen: attention plans its splits for the
 context limit (each token still cuts its own key range evenly).
 """
 from __future__ import annotations
+
+import gc
 
 import numpy as np
 import torch
@@ -22,17 +28,26 @@ from ..parts import StepBatch
 from .batch import _pad4
 
 
+def forward_step(model, cache: SequenceCache, sampled_ids: torch.Tensor, batch: StepBatch):
+    """One step of `model` on a packed batch: tokens that name a source are
+    first taken from the sampler's ids on the device."""
+    from .. import kernels
+    if batch.any_source:
+        kernels.select_tokens(batch.tokens, batch.tok_src, sampled_ids)
+    return model.forward(batch, cache)
+
+
 class DecodeGraph:
     RING = 4
 
-    def __init__(self, model, cache: SequenceCache, runtime, B: int):
-        self.model, self.cache, self.B = model, cache, B
+    def __init__(self, model, cache: SequenceCache, sampled_ids: torch.Tensor, runtime, B: int):
+        self.model, self.cache, self.sampled_ids, self.B = model, cache, sampled_ids, B
         dev = runtime.device
         self.widths = []
         for g in cache.groups:
             full = -(-runtime.max_context // g.book.page_tokens)
             self.widths.append(min(full, g.book.ring_pages) if g.book.ring_pages else full)
-        seg = [B, B, B, B + 1, B, B, B, B] + [B * w for w in self.widths]
+        seg = [B, B, B, B + 1, B, B, B, B, B] + [B * w for w in self.widths]
         self.offs, total = [], 0
         for s in seg:
             self.offs.append(total)
@@ -57,9 +72,9 @@ class DecodeGraph:
             n_tokens=B, n_seqs=B, tokens=seg_view(0, B), tok_seq=seg_view(1, B), tok_pos=seg_view(2, B),
             cu_seqlens=seg_view(3, B + 1), slots=seg_view(4, B), start_pos=seg_view(5, B), new_lens=seg_view(6, B),
             logit_rows=seg_view(7, B), n_logit_rows=B,
-            block_tables=[(seg_view(8 + gi, B * w), w) for gi, w in enumerate(self.widths)],
+            block_tables=[(seg_view(9 + gi, B * w), w) for gi, w in enumerate(self.widths)],
             host_slots=[0] * B, host_start=[1] * B, host_lens=[1] * B, packed_bytes=total * 4,
-            plan_max_len=runtime.max_context)
+            plan_max_len=runtime.max_context, tok_src=seg_view(8, B), any_source=True)
         self.graph = None
         self.logits = None
         self.kernels_per_replay = 0
@@ -77,6 +92,7 @@ class DecodeGraph:
         slots = [r.slot for r in rows]
         starts = [cache.length(s) for s in slots]
         a[o[0]:o[0] + B] = [r.tokens[0] for r in rows]
+        a[o[8]:o[8] + B] = [-1 if r.source is None else r.source for r in rows]
         a[o[2]:o[2] + B] = starts
         a[o[4]:o[4] + B] = slots
         a[o[5]:o[5] + B] = starts
@@ -92,7 +108,7 @@ class DecodeGraph:
                 if last[0] is not pages or last[1] != len(pages):
                     table[b, :len(pages)] = pages
                     seen[b] = (pages, len(pages))
-            a[o[8 + gi]:o[8 + gi] + B * w] = table.reshape(-1)
+            a[o[9 + gi]:o[9 + gi] + B * w] = table.reshape(-1)
         self.batch.host_slots = slots
         self.dev.copy_(h, non_blocking=True)
         ev = torch.cuda.Event()
@@ -100,23 +116,35 @@ class DecodeGraph:
         self.events[i] = ev
         return h
 
-    def run(self, rows) -> torch.Tensor:
+    def run(self, rows, keep: bool = True) -> torch.Tensor:
         """Runs one decode step for `rows` (already reserved in the cache);
-        returns float32 logits [B, vocab] (a copy of the graph's static output)."""
+        returns float32 logits [B, vocab]: a copy of the graph's static output,
+        or with `keep` False that output itself, which the next step overwrites."""
         from .. import kernels
         self._fill(rows)
         if self.graph is None:
-            # first use: one plain run to warm allocators and libraries, then the capture of a second run
-            # (both write the same cache rows with the same values)
+            # First use: the step runs once, launched kernel by kernel (which also warms allocators and
+            # libraries), and is then captured for the steps to come.  Capturing runs nothing, so a part
+            # with state of its own advances it once, like in every other step.
             n0 = kernels.launches[0]
-            self.model.forward(self.batch, self.cache)
+            logits = forward_step(self.model, self.cache, self.sampled_ids, self.batch)
             self.kernels_per_replay = kernels.launches[0] - n0
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self.logits = self.model.forward(self.batch, self.cache)
+            # No garbage collection while the stream captures: collecting an older engine's graphs would
+            # destroy them, which CUDA does not permit during a capture and which would invalidate this one.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g):
+                    self.logits = forward_step(self.model, self.cache, self.sampled_ids, self.batch)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             kernels.launches[0] -= self.kernels_per_replay     # capturing launched nothing
             self.graph = g
+            return logits
         self.graph.replay()
         kernels.launches[0] += self.kernels_per_replay
-        return self.logits.clone()
+        return self.logits.clone() if keep else self.logits

@@ -23,7 +23,8 @@ from ..parts import Runtime
 from ..weights import load_tensors, random_tensors
 from ..weights.random_init import storage_dtype
 from .batch import StepRow, build_step_batch
-from .decode_graph import DecodeGraph
+from .decode_graph import DecodeGraph, forward_step
+from .readback import SampledIds
 from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -50,13 +51,19 @@ class Engine:
         self.steps_run = 0
         self.use_graphs = model.graph_capturable      # replay captured CUDA graphs for decode steps
         self._decode_graphs: dict[int, "DecodeGraph"] = {}
-        self._replays_unchecked = 0                   # replayed decode steps since the kernels' status word was read
         self.h2d_bytes = 0            # bytes of step inputs copied to the device so far
+        self.sampled = SampledIds(runtime.device)     # where the sampler's ids go; rows may name them as source
 
     # ---- construction -------------------------------------------------------
     @classmethod
     def _build(cls, config_dict: dict, tensors_for, *, dtype, device, max_tokens: Optional[int],
-               max_slots: Optional[int], max_context: Optional[int]) -> "Engine":
+               max_slots: Optional[int], max_context: Optional[int], window_chunk: int = 64) -> "Engine":
+        """`window_chunk`: the most tokens a step may add to a sequence that it
+        continues (a portion of a prompt, a prompt beside decoding rows) in a
+        layer with a sliding window; such a layer keeps window + window_chunk - 1
+        keys per sequence, rounded up to whole pages."""
+        if window_chunk < 1:
+            raise ValueError("window_chunk must be at least 1")
         if dtype not in _DTYPES:
             raise ValueError(f"dtype must be 'bfloat16' or 'float32', not {dtype!r}")
         mode = _DTYPES[dtype]
@@ -77,18 +84,18 @@ class Engine:
             max_tokens = (max_slots or 1) * _round_up(max_context, PAGE_TOKENS)
         if max_slots is None:
             max_slots = max(1, -(-max_tokens // PAGE_TOKENS))
-        runtime = Runtime(device=dev, act_dtype=mode, max_context=max_context,
-                          sm_count=torch.cuda.get_device_properties(dev).multi_processor_count)
+        runtime = Runtime(device=dev, act_dtype=mode, max_context=max_context, window_chunk=window_chunk)
         with torch.cuda.device(dev):
             model.bind(tensors_for(model, mode, dev), runtime)
             kv_req, state_req = model.cache_requests()
             cache = SequenceCache(kv_req, state_req, max_tokens=max_tokens, max_slots=max_slots,
-                                  max_length=max_context, dtype=mode, device=dev)
+                                  max_length=max_context, dtype=mode, device=dev, window_slack=window_chunk - 1)
         return cls(model, cfg, config_dict, runtime, cache)
 
     @classmethod
     def from_folder(cls, folder: str, *, dtype="bfloat16", device="cuda:0", max_tokens: Optional[int] = None,
-                    max_slots: Optional[int] = None, max_context: Optional[int] = None) -> "Engine":
+                    max_slots: Optional[int] = None, max_context: Optional[int] = None,
+                    window_chunk: int = 64) -> "Engine":
         """Loads config.json and the safetensors files of `folder`."""
         config_dict = read_config_json(folder)
 
@@ -97,12 +104,12 @@ class Engine:
             return load_tensors(folder, expected, model.ignored_weights(), mode=mode, device=dev)
 
         return cls._build(config_dict, tensors_for, dtype=dtype, device=device, max_tokens=max_tokens,
-                          max_slots=max_slots, max_context=max_context)
+                          max_slots=max_slots, max_context=max_context, window_chunk=window_chunk)
 
     @classmethod
     def from_random(cls, config_dict: dict, seed: int = 0, *, dtype="bfloat16", device="cuda:0",
                     max_tokens: Optional[int] = None, max_slots: Optional[int] = None,
-                    max_context: Optional[int] = None) -> "Engine":
+                    max_context: Optional[int] = None, window_chunk: int = 64) -> "Engine":
         """Random weights generated on the device (same rules as the folder
         written by `write_model_folder`, without the trip through a file)."""
         def tensors_for(model: DecoderModel, mode, dev):
@@ -114,7 +121,7 @@ class Engine:
             return out
 
         return cls._build(config_dict, tensors_for, dtype=dtype, device=device, max_tokens=max_tokens,
-                          max_slots=max_slots, max_context=max_context)
+                          max_slots=max_slots, max_context=max_context, window_chunk=window_chunk)
 
     # ---- sequences ----------------------------------------------------------
     def new_sequence(self) -> int:
@@ -129,12 +136,20 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step -----------------------------------------------------------
-    def step(self, rows: Sequence[StepRow]) -> Optional[torch.Tensor]:
+    def _forward(self, batch):
+        """One step of the model on a packed batch: tokens that name a source
+        are first taken from the sampler's ids on the device."""
+        return forward_step(self.model, self.cache, self.sampled.ids, batch)
+
+    def step(self, rows: Sequence[StepRow], *, keep_logits: bool = True, check: bool = True) -> Optional[torch.Tensor]:
         """Runs one step.  Every row brings >= 1 token; its tokens follow what
         the row's slot already holds.  Returns float32 logits [wanted, vocab]
         on the device, in the order of the rows and of each row's `want`
-        (None if nothing is wanted).  Nothing is changed if the step is
-        refused."""
+        (None if nothing is wanted).  With `keep_logits` False the result may
+        be a buffer that the next step overwrites; with `check` False the step
+        does not wait for the device to read the kernels' status word (the
+        caller calls check_status() before using the result).  A step that is refused, or
+        that fails, changes nothing: lengths stay and the pages it took go back."""
         rows = list(rows)
         if not rows:
             raise StepError("a step needs at least one row")
@@ -142,9 +157,13 @@ class Engine:
         for r in rows:
             if not r.tokens:
                 raise StepError(f"slot {r.slot}: Empty prompt")          # src/engine.rs:347-349
-            bad = [t for t in r.tokens if not 0 <= int(t) < V]
-            if bad:
-                raise StepError(f"slot {r.slot}: token id {bad[0]} is outside the vocabulary (0..{V - 1})")
+            if r.source is not None:
+                if len(r.tokens) != 1 or not 0 <= r.source < self.sampled.rows:
+                    raise StepError(f"slot {r.slot}: a row fed from the sampler brings exactly one token")
+            else:
+                bad = [t for t in r.tokens if not 0 <= int(t) < V]
+                if bad:
+                    raise StepError(f"slot {r.slot}: token id {bad[0]} is outside the vocabulary (0..{V - 1})")
             for w in r.want:
                 if not 0 <= w < len(r.tokens):
                     raise StepError(f"slot {r.slot}: wanted place {w} is outside the {len(r.tokens)} tokens brought")
@@ -158,27 +177,36 @@ class Engine:
             self.cache.reserve(slots, lens)
         except CacheError as e:
             raise StepError(str(e)) from e
-        with torch.cuda.device(self.runtime.device):
-            if self.use_graphs and all(n == 1 for n in lens) and all(r.want == [0] for r in rows):
-                graph = self._decode_graphs.get(len(rows))
-                if graph is None:
-                    graph = self._decode_graphs[len(rows)] = DecodeGraph(self.model, self.cache, self.runtime,
-                                                                         len(rows))
-                logits = graph.run(rows)
-                self.h2d_bytes += graph.batch.packed_bytes
-                self._replays_unchecked += 1
-                if self._replays_unchecked >= 256:      # the check waits for the device: now and then is enough
-                    self._replays_unchecked = 0
-                    kernels.mark_tc_launched()
-                    kernels.check_tc_status()
-            else:
-                batch = build_step_batch(rows, self.cache, self.runtime.device)
-                logits = self.model.forward(batch, self.cache)
-                self.h2d_bytes += batch.packed_bytes
-                kernels.check_tc_status()      # a tensor-core product that gave up on a wait must not pass silently
+        try:
+            with torch.cuda.device(self.runtime.device):
+                if self.use_graphs and all(n == 1 for n in lens) and all(r.want == [0] for r in rows):
+                    graph = self._decode_graphs.get(len(rows))
+                    if graph is None:
+                        graph = self._decode_graphs[len(rows)] = DecodeGraph(
+                            self.model, self.cache, self.sampled.ids, self.runtime, len(rows))
+                    logits = graph.run(rows, keep_logits)
+                    self.h2d_bytes += graph.batch.packed_bytes
+                    kernels.mark_tc_launched()      # read with the sampled ids, or by check_status()
+                else:
+                    batch = build_step_batch(rows, self.cache, self.runtime.device)
+                    logits = self._forward(batch)
+                    self.h2d_bytes += batch.packed_bytes
+                    if check:
+                        kernels.check_tc_status()   # a product that gave up on a wait must not pass silently
+        except BaseException:
+            self.cache.trim(slots)              # the pages taken for this step go back; lengths were not touched
+            raise
         self.cache.commit(slots, lens)
         self.steps_run += 1
         return logits
+
+    def check_status(self) -> None:
+        """Raises if a kernel of an earlier step gave up on a bounded wait
+        (waits for the device).  Replayed decode steps do not check by
+        themselves: the generation loop reads the status word with every
+        step's sampled ids, and whoever else replays steps calls this before
+        it uses their results."""
+        kernels.check_tc_status()
 
     # ---- generation (see generate.py) ----------------------------------------
     def generate(self, prompts, params=None, **kwargs):

@@ -12,6 +12,7 @@ from typing import Optional
 
 import torch
 
+from .. import kernels
 from ..cache import KVLayerView, KVRequest, SequenceCache, StateRequest
 from ..config import ConfigError, ModelSpec
 from ..parts import Runtime, StepBatch, StepContext, WeightSpec, make_block, make_part
@@ -99,6 +100,7 @@ class DecoderModel:
         logits [wanted rows, vocab] (None if no row is wanted)."""
         rt = self.runtime
         h = self.embedding.forward(batch.tokens)
+        kernels.mark("embed")
         for i, e in enumerate(self.spec.schedule):
             owner = i if e.cache_of is None else e.cache_of
             ctx = StepContext(batch=batch, runtime=rt, entry=i)
@@ -113,4 +115,6 @@ class DecoderModel:
         if batch.n_logit_rows == 0:
             return None
         normed = self.final_norm.forward(h, rt.act_dtype, rows=batch.logit_rows)
-        return self.head.forward(normed)
+        logits = self.head.forward(normed)
+        kernels.mark("head")
+        return logits

@@ -59,6 +59,7 @@ def replay(engine: Engine, lines: Iterable[str], out_dir: str, done: IO[str] = s
                 for rid in new_ids:            # a refused step leaves nothing behind
                     engine.release(slots.pop(rid))
                 raise
+            engine.check_status()              # no logits leave here from a kernel that gave up on a wait
             if logits is not None:
                 arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
                 arr.tofile(os.path.join(out_dir, f"{step}.f32"))

@@ -47,31 +47,79 @@ def stream() -> int:
 launches = [0]
 
 
+class Timeline:
+    """Device time by class of work.  While a timeline is the module's `timeline`, the parts call `mark(label)`
+    after the kernels of a class (q/k/v product, attention, ...), which records a CUDA event; `totals()` then
+    gives the time between consecutive marks, summed by label.  The marks sit between kernels, so a kernel does
+    not start under its predecessor's tail across a mark (dependent launch); the sum of the classes is therefore
+    a little more than the step takes when it is replayed as a graph.  The caller must keep the device busy
+    ahead of the step (see bench.py), or the marks measure the host's launch pace instead of the kernels."""
+
+    def __init__(self):
+        self.marks: list = []
+
+    def mark(self, label: str) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.marks.append((label, ev))
+
+    def totals(self) -> dict:
+        torch.cuda.synchronize()
+        out: dict = {}
+        for (_, a), (label, b) in zip(self.marks, self.marks[1:]):
+            out[label] = out.get(label, 0.0) + a.elapsed_time(b) * 1e3        # microseconds
+        return out
+
+
+timeline = None          # a Timeline while one is recording
+
+
+def mark(label: str) -> None:
+    """Ends a class of work on the recording timeline, if there is one."""
+    if timeline is not None:
+        timeline.mark(label)
+
+
 def check(status: int, what: str, n_kernels: int = 1) -> None:
     if status != 0:
         raise KernelError(f"{what}: CUDA error {status}" + (" (invalid argument)" if status == 1 else ""))
     launches[0] += n_kernels
 
 
-# ---- the status word of the tcgen05 kernels ---------------------------------------
-# Their mbarrier waits are bounded; a wait that runs out raises a bit in this device word instead of hanging
-# (2: a matrix product, 4: the prompt attention, 8: its shared memory was not aligned).
-_tc_status: dict = {}               # device -> int32[1]
+# ---- the report buffer: the status word of the tcgen05 kernels and the sampled ids --
+# One int32 buffer per device.  Word 0 is the status word: the mbarrier waits of the tcgen05 kernels are bounded,
+# and a wait that runs out raises a bit here instead of hanging (2: a matrix product, 4: the prompt attention,
+# 8: its shared memory was not aligned).  Words 1.. take the token ids the sampler chooses, so that one small
+# device-to-host copy per step brings both the ids and the status to the host.
+REPORT_ROWS = 4096
+_report: dict = {}                  # device -> int32[1 + REPORT_ROWS]
 _tc_launched = [0]
+
+
+def report_buffer(device) -> torch.Tensor:
+    t = _report.get(device)
+    if t is None:
+        t = _report[device] = torch.zeros(1 + REPORT_ROWS, dtype=torch.int32, device=device)
+    return t
 
 
 def tc_status_word(device) -> torch.Tensor:
     """The device word a tcgen05 kernel launched now reports into; notes that one was launched."""
-    t = _tc_status.get(device)
-    if t is None:
-        t = _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
     _tc_launched[0] += 1
-    return t
+    return report_buffer(device)[:1]
 
 
 def mark_tc_launched() -> None:
     """Replayed graphs launch tcgen05 kernels without passing through tc_status_word(): the caller says so."""
     _tc_launched[0] += 1
+
+
+def raise_on_status(value: int, device) -> None:
+    """Raises for a non-zero status word that the caller has read (and clears the word on the device)."""
+    if value:
+        report_buffer(device)[:1].zero_()
+        raise KernelError(f"a tcgen05 kernel on {device}: a pipeline wait ran out (status {value}); "
+                          "results are invalid")
 
 
 def check_tc_status() -> None:
@@ -80,15 +128,14 @@ def check_tc_status() -> None:
     if not _tc_launched[0]:
         return
     _tc_launched[0] = 0
-    for dev, t in _tc_status.items():
-        v = int(t.item())
-        if v:
-            t.zero_()
-            raise KernelError(f"a tcgen05 kernel on {dev}: a pipeline wait ran out (status {v}); results are invalid")
+    for dev, t in _report.items():
+        raise_on_status(int(t[0].item()), dev)
 
 
 _SIGNATURES = {
     "tq_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tq_select_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "tq_random_fill": [c_void_p, c_int, c_size_t, ctypes.c_ulonglong, c_float, c_float, c_void_p],
     "tq_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
     "tq_qkv_rope_cache": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

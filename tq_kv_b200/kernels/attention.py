@@ -23,7 +23,7 @@ def check_head_geometry(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
         raise KernelError(f"attention: more than 65535 key/value heads ({n_kv_heads})")
 
 
-def plan_splits(n_tokens: int, n_kv_heads: int, max_keys: int, sm_count: int = 148) -> int:
+def plan_splits(n_tokens: int, n_kv_heads: int, max_keys: int, sm_count: int) -> int:
     """Number of splits of the key range for a step: one while the grid fills
     the GPU or the key ranges are short, else as many as fill the GPU in one
     wave, with at least 128 keys per split of the longest range.  (Each

@@ -85,3 +85,28 @@ def add_into(acc: torch.Tensor, x: torch.Tensor):
     need_contiguous(acc=acc, x=x)
     check(core().tq_add_into(ptr(acc), ptr(x), dtype_code(x), acc.numel(), stream()), "add_into")
     return acc
+
+
+def select_tokens(tokens: torch.Tensor, source_rows: torch.Tensor, sampled: torch.Tensor):
+    """tokens[i] = sampled[source_rows[i]] where source_rows[i] >= 0; other
+    entries keep the id the host put there.  All int32, on the device: the
+    token a sequence decodes next can be the one the sampler just chose,
+    without a trip through the host."""
+    n = tokens.shape[0]
+    for name, t in (("tokens", tokens), ("source_rows", source_rows), ("sampled", sampled)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"select_tokens: {name} must be int32")
+    if source_rows.shape[0] < n:
+        raise KernelError("select_tokens: one source row per token")
+    need_contiguous(tokens=tokens, source_rows=source_rows, sampled=sampled)
+    check(core().tq_select_tokens(ptr(tokens), ptr(source_rows), ptr(sampled), n, stream()), "select_tokens")
+    return tokens
+
+
+def random_fill(out: torch.Tensor, key: int, std: float, offset: float = 0.0):
+    """out[i] = offset + std * z(key, i) with z standard normal from the
+    counter-based generator of csrc/random_fill.cu (float32 or bfloat16 out)."""
+    need_contiguous(out=out)
+    check(core().tq_random_fill(ptr(out), dtype_code(out), out.numel(), int(key) & ((1 << 64) - 1), float(std),
+                                float(offset), stream()), "random_fill")
+    return out

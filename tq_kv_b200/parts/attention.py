@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from ..cache import PAGE_TOKENS, KVRequest
+from ..cache import PAGE_TOKENS, KVRequest, ring_pages_for
 from .base import Mixer, Runtime, StepContext, WeightSpec, float32_vector
 from .registry import make_part
 
@@ -38,6 +38,7 @@ class GQAttention(Mixer):
         self.q_width = self.n_heads * self.head_dim
         self.kv_width = self.n_kv_heads * self.head_dim
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+        self.window_chunk = 1
 
     # ---- weights ----------------------------------------------------------
     def _n(self, which: str, leaf: str) -> str:
@@ -68,6 +69,7 @@ class GQAttention(Mixer):
             self.b_qkv = torch.cat([float32_vector(tensors[self._n(x, "bias")]) for x in "qkv"]).contiguous()
         if self.out_bias:
             self.b_o = float32_vector(tensors[self._n("o", "bias")])
+        self.window_chunk = runtime.window_chunk
         self.position.bind(tensors, runtime, shared)      # a position encoding may have tensors of its own
         self.position.prepare(runtime, shared)
 
@@ -83,12 +85,13 @@ class GQAttention(Mixer):
     def check_step(self, start_pos, step_lens, owns_cache):
         if self.window is None or self._use_packed(start_pos, step_lens, owns_cache):
             return
-        ring_tokens = -(-self.window // PAGE_TOKENS) * PAGE_TOKENS
+        ring_tokens = ring_pages_for(self.window, self.window_chunk - 1) * PAGE_TOKENS
         longest = max(step_lens)
         if longest > ring_tokens - self.window + 1:
             raise kernels.KernelError(
                 f"a layer with a window of {self.window} keeps {ring_tokens} keys per sequence and cannot continue "
-                f"a sequence by {longest} tokens in one step (at most {ring_tokens - self.window + 1})")
+                f"a sequence by {longest} tokens in one step (at most {ring_tokens - self.window + 1}; the engine's "
+                f"window_chunk option sets this)")
 
     # ---- one step -----------------------------------------------------------
     def forward(self, x, ctx: StepContext, residual):
@@ -98,11 +101,13 @@ class GQAttention(Mixer):
         owns = kv is not None and kv.writes
         packed = self._use_packed(b.host_start, b.host_lens, owns)
         qkv = kernels.linear(x, self.w_qkv, out_dtype=torch.float32)
+        kernels.mark("qkv")
         q = torch.empty((T, self.q_width), dtype=act, device=dev)
         k = torch.empty((T, self.kv_width), dtype=act, device=dev) if packed else None
         v = torch.empty((T, self.kv_width), dtype=act, device=dev) if packed else None
         self.position.encode_and_store(qkv, self.b_qkv, ctx, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
                                        head_dim=self.head_dim, q_out=q, k_out=k, v_out=v)
+        kernels.mark("rotary")
         out = torch.empty_like(q)
         common = dict(n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
                       tok_pos=b.tok_pos, tok_seq=b.tok_seq, cu_seqlens=b.cu_seqlens, start_pos=b.start_pos,
@@ -119,4 +124,6 @@ class GQAttention(Mixer):
             kernels.attention(q, out, k_pages=kv.k_pages, v_pages=kv.v_pages, block_table=kv.block_table,
                               table_width=kv.table_width, ring_pages=kv.ring_pages, page_tokens=kv.page_tokens,
                               n_splits=n_splits, scratch=scratch, **common)
+        kernels.mark("attention")
         kernels.linear(out, self.w_o, bias=self.b_o, out=residual, accumulate=True)
+        kernels.mark("o")

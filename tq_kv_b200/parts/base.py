@@ -45,7 +45,12 @@ class Runtime:
     device: torch.device
     act_dtype: torch.dtype
     max_context: int
-    sm_count: int = 148
+    sm_count: int = 0                 # streaming multiprocessors of the device (the engine fills it in)
+    window_chunk: int = 64            # tokens a windowed layer accepts in one step that continues a sequence
+
+    def __post_init__(self):
+        if not self.sm_count and self.device.type == "cuda" and torch.cuda.is_available():
+            self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
 
 @dataclass
@@ -69,6 +74,8 @@ class StepBatch:
     host_lens: list[int] = field(default_factory=list)      # tokens each row brings
     packed_bytes: int = 0                                    # size of the one host-to-device copy
     plan_max_len: int = 0      # if > 0: the length to plan for instead of this step's own (replayed graphs)
+    tok_src: Optional[torch.Tensor] = None    # [T] row of the sampler's last ids that holds the token, or -1
+    any_source: bool = False                  # some token comes from the sampler's ids on the device
 
     @property
     def all_from_zero(self) -> bool:

@@ -4,6 +4,7 @@ h += feed_forward(norm2(h)), with the sums done in float32 on the residual
 stream."""
 from __future__ import annotations
 
+from .. import kernels
 from ..config import LayerSpec
 from .base import StepContext
 from .registry import make_part
@@ -22,5 +23,9 @@ class PrenormResidualBlock:
 
     def forward(self, h, ctx: StepContext) -> None:
         act = ctx.runtime.act_dtype
-        self.mixer.forward(self.mixer_norm.forward(h, act), ctx, h)
-        self.feed_forward.forward(self.feed_forward_norm.forward(h, act), ctx, h)
+        x = self.mixer_norm.forward(h, act)
+        kernels.mark("norms")
+        self.mixer.forward(x, ctx, h)
+        x = self.feed_forward_norm.forward(h, act)
+        kernels.mark("norms")
+        self.feed_forward.forward(x, ctx, h)

@@ -34,4 +34,6 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx: StepContext, residual):
         act = kernels.linear(x, self.w_gate_up, swiglu=True, out_dtype=ctx.runtime.act_dtype)
+        kernels.mark("gate_up")
         kernels.linear(act, self.w_down, out=residual, accumulate=True)
+        kernels.mark("down")

@@ -2,7 +2,7 @@
 
 `Sampler.sample(logits, requests, index)` applies the repeat penalty, then
 arg-max or temperature / top-k / top-p (csrc/sampling.cu), and returns the
-chosen tokens as a host list.  The occurrence counts the penalty needs are
+chosen tokens as a host list; `sample_device` leaves them on the device.  The occurrence counts the penalty needs are
 per-row state held here; `keep(rows)` drops the rows of finished requests.
 
 Reference: src/engine.rs:353-362 (choice of sampler), :403-419 (penalty over
@@ -21,6 +21,7 @@ from .rng import uniform
 
 
 class Sampler:
+    U_RING = 8
     def __init__(self, params: GenerationParams, n_rows: int, vocab_size: int, device):
         params.validate()
         self.params = params
@@ -33,6 +34,9 @@ class Sampler:
         self.out = torch.zeros(n_rows, dtype=torch.int32, device=self.device)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self._cap = n_rows
+        self._u_host = self._u_dev = self._u_events = None
+        self._u_turn = 0
 
     def keep(self, rows: Sequence[int]) -> None:
         """Keeps the given rows (indices into the current rows), in order."""
@@ -41,23 +45,52 @@ class Sampler:
             idx = torch.tensor(list(rows), dtype=torch.long, device=self.device)
             self.counts = self.counts.index_select(0, idx).contiguous()
 
-    def sample(self, logits: torch.Tensor, requests: Sequence[int], index: int) -> list[int]:
-        """One token per row.  `requests[r]` is the request index of row r and
-        `index` the number of tokens sampled for these requests so far; the two
-        select the row's uniform draw."""
+    def _uniforms(self, requests: Sequence[int], index: int) -> torch.Tensor:
+        """The rows' draws for sampled token `index`, copied to the device from a
+        small ring of pinned buffers (a buffer is reused only after several later
+        draws, by when the kernel that read it has long run)."""
+        R = len(requests)
+        if self._u_host is None:
+            self._u_host = [torch.zeros(self._cap, dtype=torch.float32).pin_memory()
+                            if self.device.type == "cuda" else torch.zeros(self._cap, dtype=torch.float32)
+                            for _ in range(self.U_RING)]
+            self._u_dev = [torch.zeros(self._cap, dtype=torch.float32, device=self.device)
+                           for _ in range(self.U_RING)]
+            self._u_events = [None] * self.U_RING
+        i = self._u_turn % self.U_RING
+        self._u_turn += 1
+        if self._u_events[i] is not None:
+            self._u_events[i].synchronize()
+        p = self.params
+        self._u_host[i][:R] = torch.tensor([uniform(p.seed, r, index) for r in requests], dtype=torch.float32)
+        self._u_dev[i][:R].copy_(self._u_host[i][:R], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self._u_events[i] = ev
+        self.h2d_bytes += 4 * R
+        return self._u_dev[i]
+
+    def sample_device(self, logits: torch.Tensor, requests: Sequence[int], index: int,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One token per row, left on the device in `out` (int32, at least R
+        long; the sampler's own buffer if none is given).  `requests[r]` is the
+        request index of row r and `index` the number of tokens sampled for
+        these requests so far; the two select the row's uniform draw."""
         p = self.params
         R = logits.shape[0]
         if R != self.n_rows or len(requests) != R:
             raise ValueError(f"sampler holds {self.n_rows} rows, got logits for {R}")
-        uniforms = None
-        if p.temperature > 0:
-            u = torch.tensor([uniform(p.seed, r, index) for r in requests], dtype=torch.float32)
-            if self.device.type == "cuda":
-                u = u.pin_memory()
-            uniforms = u.to(self.device, non_blocking=True)
-            self.h2d_bytes += 4 * R
-        kernels.sample(logits, self.out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
+        out = self.out if out is None else out
+        uniforms = self._uniforms(requests, index) if p.temperature > 0 else None
+        kernels.sample(logits, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                        uniforms=uniforms, counts=self.counts[:R] if self.counts is not None else None,
                        repeat_penalty=p.repeat_penalty)
+        return out
+
+    def sample(self, logits: torch.Tensor, requests: Sequence[int], index: int) -> list[int]:
+        """As sample_device(), with the chosen tokens brought to the host."""
+        R = logits.shape[0]
+        out = self.sample_device(logits, requests, index)
         self.d2h_bytes += 4 * R
-        return self.out[:R].tolist()
+        return out[:R].tolist()
