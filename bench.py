@@ -10,7 +10,8 @@ launched back to back (tokens are given, nothing waits for the host).  `e2e`
 is the same through the Python entry point `Engine.generate()`: prompts go in
 as host token ids and every step's token ids come back to the host (the loop
 reads them one step late, while the device runs the next step); it runs for
-at least 128 steps whatever K is, and `e2e.steps` names the count.  `prefill`
+at least 128 timed steps whatever K is, after warm-up steps as the device-timed
+run has them (`e2e.steps`, `e2e.warmup`).  `prefill`
 is one step over a 2,048-token prompt; `roofline` relates the decode step's
 necessary bytes (every weight it uses once, the cache of the live sequences)
 to its time; `points` hold decode at batch 1 and 64, device-timed and end to
@@ -229,7 +230,7 @@ def main() -> int:
     if unequal:
         lengths = torch.randint(64, 4097, (args.batch,), generator=gen).tolist()
         max_b = args.batch
-        room = max(K + W, args.e2e_steps + 1) + 2
+        room = max(K + W, args.e2e_steps + max(W, 16) + 1) + 2
         max_tokens = sum(-(-(n + room) // 64) * 64 for n in lengths)
     else:
         lengths = None
@@ -287,8 +288,14 @@ def main() -> int:
             engine.release(s)
         return ms, launches
 
+    e2e_warmup = max(W, 16)
+
     def e2e_run(prompts: list[list[int]], steps: int):
-        """Tokens per second through Engine.generate(): host token ids in, every step's ids back on the host."""
+        """Tokens per second through Engine.generate(): host token ids in, every step's ids back on the host.
+        As in the device-timed run, the first steps after the prompts are warm-up and are not timed (right
+        after a prompt of thousands of tokens the first dozen decode steps run at the lower clocks that the
+        prompt's matrix products left behind); then `steps` steps are timed between the arrivals of their
+        tokens on the host."""
         stamps: list[float] = []
         last = len(prompts) - 1
 
@@ -297,17 +304,18 @@ def main() -> int:
                 stamps.append(time.perf_counter())         # the token is on the host now
 
         h2d0, stats = engine.h2d_bytes, {}
-        engine.generate(prompts, tq.GenerationParams.greedy(steps + 1, stop_token_ids=()), on_token=on_token,
-                        stats=stats)
+        engine.generate(prompts, tq.GenerationParams.greedy(e2e_warmup + steps + 1, stop_token_ids=()),
+                        on_token=on_token, stats=stats)
+        timed = stamps[e2e_warmup:]
         n = len(stamps)
-        value = len(prompts) * (n - 1) / (stamps[-1] - stamps[0])
+        value = len(prompts) * (len(timed) - 1) / (timed[-1] - timed[0])
         h2d = (engine.h2d_bytes - h2d0 + stats.get("h2d_bytes", 0)) / n
-        return value, int(h2d), int(stats.get("d2h_bytes", 0) / n), n - 1
+        return value, int(h2d), int(stats.get("d2h_bytes", 0) / n), len(timed) - 1
 
     def e2e_prompt(steps: int) -> int:
         """Prompt length at which `steps` generated tokens see the same mean context as the device-timed steps."""
-        want = start_ctx + W + K / 2 - steps / 2
-        return int(max(args.prompt, min(want, args.context - steps - 2)))
+        want = start_ctx + W + K / 2 - steps / 2 - e2e_warmup
+        return int(max(args.prompt, min(want, args.context - steps - e2e_warmup - 2)))
 
     def prefill_run(prompt_lens: list[int]):
         """One step over prompts of these lengths, logits at each prompt's last place; after one warm-up."""
@@ -371,12 +379,12 @@ def main() -> int:
         if unequal:
             prompts = [torch.randint(0, V, (n,), generator=gen).tolist() for n in lengths]
         else:
-            e2e_steps = min(e2e_steps, args.context - args.prompt - 1)
+            e2e_steps = min(e2e_steps, args.context - args.prompt - e2e_warmup - 2)
             prompts = [torch.randint(0, V, (e2e_prompt(e2e_steps),), generator=gen).tolist()
                        for _ in range(args.batch)]
         ev, h2d, d2h, n = e2e_run(prompts, e2e_steps)
         rec["e2e"] = {"value": round(ev, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                      "steps": n}
+                      "steps": n, "warmup": e2e_warmup}
     else:
         rec["e2e"] = {"value": 0.0, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "steps": 0}
 
@@ -394,7 +402,7 @@ def main() -> int:
                 ms_b, _ = decode_run([start_ctx] * b, steps_b, max(3, min(W, 4)))
                 points[f"decode_b{b}"] = round(b * steps_b / (ms_b / 1e3), 1)
                 if not args.no_e2e:
-                    n_e2e = min(args.e2e_steps, args.context - args.prompt - 1)
+                    n_e2e = min(args.e2e_steps, args.context - args.prompt - e2e_warmup - 2)
                     prompts = [torch.randint(0, V, (e2e_prompt(n_e2e),), generator=gen).tolist() for _ in range(b)]
                     points[f"e2e_b{b}"] = round(e2e_run(prompts, n_e2e)[0], 1)
             rec["points"] = points

@@ -111,3 +111,27 @@ def test_named_shapes_are_valid_configs():
         Qwen2Config.from_dict(named_shape(n))
     with pytest.raises(KeyError):
         named_shape("nope")
+
+
+def test_head_sizes_the_kernels_do_not_take_are_refused_where_the_config_is_read():
+    from helpers import TINY_A
+    from tq_kv_b200.config import ConfigError, Qwen2Config
+    for hd in (8, 24, 40, 272):
+        with pytest.raises(ConfigError, match="head_dim"):
+            Qwen2Config.from_dict({**TINY_A, "head_dim": hd})
+    for hd in (16, 48, 112, 256):
+        assert Qwen2Config.from_dict({**TINY_A, "head_dim": hd}).head_dim == hd
+
+
+def test_a_layer_names_its_parts_and_a_missing_one_is_named_in_the_error():
+    from dataclasses import replace
+    from helpers import TINY_A
+    from tq_kv_b200.config import ConfigError, PartSpec, Qwen2Config, build_qwen2_spec
+    layer = build_qwen2_spec(Qwen2Config.from_dict(TINY_A)).layers[0]
+    assert list(layer.parts()) == ["mixer_norm", "mixer", "feed_forward_norm", "feed_forward"]
+    more = replace(layer, extra_parts={"after": PartSpec("rms_norm", {"width": 64, "eps": 1e-6}, "x.")})
+    assert more.part("after").weights_prefix == "x." and len(more.parts()) == 5
+    with pytest.raises(ConfigError, match="needs a part named 'gate'"):
+        layer.part("gate")
+    with pytest.raises(ConfigError, match="twice"):
+        replace(layer, extra_parts={"mixer": layer.mixer}).parts()

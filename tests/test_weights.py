@@ -147,3 +147,59 @@ def test_random_weights_are_normal_with_the_roles_moments():
     assert float(z.abs().max()) < 5.8 and torch.isfinite(m).all()
     n = random_tensor("n", (4096,), "norm_scale", 1, torch.float32, "cpu").double()
     assert abs(float(n.mean()) - 1.0) < 6e-3 and abs(float(n.std()) - 0.1) < 6e-3
+
+
+def _split_into_shards(folder, tmp_path, name="sharded"):
+    """The folder's tensors in two shard files (odd and even tensors) under a new folder."""
+    import shutil
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    tensors = {n: f.read(n).clone() for n in f.entries}
+    f.close()
+    out = str(tmp_path / name)
+    os.makedirs(out)
+    shutil.copy(os.path.join(folder, "config.json"), out)
+    names = sorted(tensors)
+    parts = {"model-00001-of-00002.safetensors": names[0::2], "model-00002-of-00002.safetensors": names[1::2]}
+    for fname, ns in parts.items():
+        write_safetensors(os.path.join(out, fname), [(n, tensors[n].dtype, tuple(tensors[n].shape)) for n in ns],
+                          [(n, tensors[n]) for n in ns])
+    return out, parts, tensors
+
+
+def test_shards_are_found_by_scan_and_by_the_index(tmp_path):
+    from tq_kv_b200.weights.safetensors_io import INDEX_NAME
+    folder = write_model_folder(TINY_A, str(tmp_path / "whole"), seed=2)
+    expected, ignored = _expected(TINY_A)
+    whole = load_tensors(folder, expected, ignored, mode=torch.float32, device="cpu")
+    out, parts, tensors = _split_into_shards(folder, tmp_path)
+    scanned = load_tensors(out, expected, ignored, mode=torch.float32, device="cpu")      # no index: the folder scan
+    assert all(torch.equal(whole[n], scanned[n]) for n in whole)
+    # a tensor stored in two shards is an error of the scan ...
+    dup = sorted(tensors)[0]
+    write_safetensors(os.path.join(out, "stray.safetensors"), [(dup, tensors[dup].dtype, tuple(tensors[dup].shape))],
+                      [(dup, torch.zeros_like(tensors[dup]))])
+    with pytest.raises(SafetensorsError, match="stored twice"):
+        load_tensors(out, expected, ignored, mode=torch.float32, device="cpu")
+    # ... but with an index the weight_map decides, and the stray file is not read
+    weight_map = {n: fname for fname, ns in parts.items() for n in ns}
+    with open(os.path.join(out, INDEX_NAME), "w") as f:
+        json.dump({"metadata": {}, "weight_map": weight_map}, f)
+    indexed = load_tensors(out, expected, ignored, mode=torch.float32, device="cpu")
+    assert all(torch.equal(whole[n], indexed[n]) for n in whole)
+    # an index that places a tensor in the wrong file, or names a file that is not there, is an error
+    bad = dict(weight_map)
+    bad[dup] = [f for f in parts if f != weight_map[dup]][0]
+    with open(os.path.join(out, INDEX_NAME), "w") as f:
+        json.dump({"weight_map": bad}, f)
+    with pytest.raises(SafetensorsError, match="do not hold them"):
+        load_tensors(out, expected, ignored, mode=torch.float32, device="cpu")
+    bad = dict(weight_map)
+    bad[dup] = "model-00003-of-00002.safetensors"
+    with open(os.path.join(out, INDEX_NAME), "w") as f:
+        json.dump({"weight_map": bad}, f)
+    with pytest.raises(SafetensorsError, match="not in"):
+        load_tensors(out, expected, ignored, mode=torch.float32, device="cpu")
+    with open(os.path.join(out, INDEX_NAME), "w") as f:
+        f.write("{")
+    with pytest.raises(SafetensorsError, match="Invalid model.safetensors.index.json"):
+        load_tensors(out, expected, ignored, mode=torch.float32, device="cpu")

@@ -1,8 +1,8 @@
 """Device storage of the cache: key/value pages per group of layers and the
 fixed-size state per sequence, above the host bookkeeping of `pool.py`.
 
-Layout of a group: K and V are each `[entries, pages, kv_heads, page_tokens,
-head_dim]`.  Token position p of a sequence lives in the sequence's logical
+Layout of a group: K is `[entries, pages, kv_heads, page_tokens, head_dim]`
+and V the same with the value rows' width.  Token position p of a sequence lives in the sequence's logical
 page p // page_tokens (modulo the ring length in a window group) at row
 p % page_tokens; all layers of a group share the page numbering, so one block
 table per group and step serves every layer of the group.
@@ -24,12 +24,16 @@ PAGE_TOKENS = 64
 
 @dataclass(frozen=True)
 class KVRequest:
-    """What a mixer asks of the cache: keys and values of `n_kv_heads` heads
-    of `head_dim`, of all earlier tokens (`window` None) or of the last
-    `window` tokens."""
+    """What a mixer asks of the cache: per token and per each of `n_kv_heads`
+    heads a key row of `head_dim` values and a value row of `value_dim` values
+    (None: as wide as the key), of all earlier tokens (`window` None) or of
+    the last `window` tokens.  What the rows mean is the mixer's business: a
+    mixer that caches one latent per token asks for one head of the latent's
+    width and may leave the value rows a single column."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -44,7 +48,7 @@ class StateRequest:
 class KVLayerView:
     """What a mixer sees of the cache during one step."""
     k_pages: torch.Tensor            # [pages, kv_heads, page_tokens, head_dim]
-    v_pages: torch.Tensor
+    v_pages: torch.Tensor            # [pages, kv_heads, page_tokens, value_dim]
     block_table: torch.Tensor        # int32 [rows, table_width], physical page per logical page
     table_width: int
     ring_pages: int                  # 0: all keys are kept
@@ -71,16 +75,16 @@ class KVGroup:
         if request.window is not None:
             ring = ring_pages_for(request.window, window_slack)
         self.book = GroupPages(name, n_pages, PAGE_TOKENS, ring)
-        shape = (len(entries), n_pages, request.n_kv_heads, PAGE_TOKENS, request.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        shape = (len(entries), n_pages, request.n_kv_heads, PAGE_TOKENS)
+        self.k = torch.zeros((*shape, request.head_dim), dtype=dtype, device=device)
+        self.v = torch.zeros((*shape, request.value_dim or request.head_dim), dtype=dtype, device=device)
 
     @property
     def ring_pages(self) -> int:
         return self.book.ring_pages or 0
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class SequenceCache:

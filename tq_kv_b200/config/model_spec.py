@@ -29,13 +29,37 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: the arrangement (`block` kind) and the parts it arranges."""
+    """One layer: the arrangement (`block` kind) and the parts it arranges, by
+    name.  The four names that the pre-norm residual block uses are fields of
+    their own; a block kind with other slots (norms after the parts, a second
+    feed-forward, ...) finds them in `extra_parts` and leaves unset what it
+    does not use.  Which names a layer needs is the block kind's business:
+    `part(name)` raises for one that is missing."""
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    mixer: Optional[PartSpec] = None
+    feed_forward: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
     block_params: dict[str, Any] = field(default_factory=dict)
+    extra_parts: dict[str, PartSpec] = field(default_factory=dict)
+
+    def parts(self) -> dict[str, PartSpec]:
+        """Every part the layer names, by slot name."""
+        named = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "feed_forward_norm": self.feed_forward_norm,
+                 "feed_forward": self.feed_forward}
+        out = {k: v for k, v in named.items() if v is not None}
+        for k, v in self.extra_parts.items():
+            if k in out:
+                raise ConfigError(f"layer names the part '{k}' twice")
+            out[k] = v
+        return out
+
+    def part(self, name: str) -> PartSpec:
+        try:
+            return self.parts()[name]
+        except KeyError:
+            raise ConfigError(f"a block of kind '{self.block}' needs a part named '{name}'; "
+                              f"the layer has {sorted(self.parts())}") from None
 
 
 @dataclass(frozen=True)

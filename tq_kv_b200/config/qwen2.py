@@ -121,8 +121,9 @@ class Qwen2Config:
             raise ConfigError(
                 f"config.json: num_attention_heads {self.num_attention_heads} is not a multiple of "
                 f"num_key_value_heads {self.num_key_value_heads}")
-        if self.head_dim % 2:
-            raise ConfigError(f"config.json: head_dim {self.head_dim} must be even for rotary position encoding")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ConfigError(f"config.json: head_dim {self.head_dim} is not supported: the attention kernels take "
+                              "head sizes that are multiples of 16 from 16 to 256")
         if self.hidden_act != "silu":
             raise ConfigError(f"config.json: hidden_act '{self.hidden_act}' is not supported (silu only)")
         if self.use_sliding_window:

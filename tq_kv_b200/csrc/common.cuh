@@ -108,6 +108,20 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 static inline int tq_launch_status() { return (int)cudaGetLastError(); }
 
+// Streaming multiprocessors of the current device (asked once per device): grids and splits are sized by it.
+static inline int tq_sm_count() {
+    static int counts[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!counts[dev]) {
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        counts[dev] = sms > 0 ? sms : 1;
+    }
+    return counts[dev];
+}
+
 // TQ_DETERMINISTIC=1: no product is cut along K into shares that meet in memory in arrival order (the tcgen05
 // products then run somewhat slower: fewer blocks where tiles are few).  Every sum is then made in a fixed
 // order, and two runs of the same steps give the same bits.

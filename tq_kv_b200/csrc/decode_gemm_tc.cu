@@ -394,13 +394,7 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
     // Float32 results without gating whose tiles do not fill the GPU's block slots (two per SM): independent
     // shares of K of at least 8 steps, as many as still run in one wave, summed by TMA.  Y must be fit for TMA
     // (16-byte aligned base and row stride).
-    static int slots = 0;
-    if (!slots) {
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        slots = 2 * (sms > 0 ? sms : 1);
-    }
+    const int slots = 2 * tq_sm_count();
     if (!SWIGLU && sizeof(TO) == 4 && k_total >= 16 && !tq_deterministic() &&
         (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (ldy & 3) == 0) {
         int splits = slots / tiles;
@@ -410,7 +404,7 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
     }
     // split K while the grid is small and the shares stay long.  Measured best on the 7B shapes: up to 4
     // blocks and about 64 blocks in all for batches over 16 rows, up to 8 and a full GPU for smaller ones.
-    const int max_ranks = M > 16 ? 4 : 8, want_blocks = M > 16 ? 64 : 148;
+    const int max_ranks = M > 16 ? 4 : 8, want_blocks = M > 16 ? 64 : tq_sm_count();
     int ranks = 1;
     while (ranks < max_ranks && tiles * ranks < want_blocks && k_total / (ranks * 2) >= 4) ranks *= 2;
     return dg_launch_s<MP, SWIGLU, TO, 4>(mw, mx, bias, Y, M, N, K, ldy, accumulate, status, ranks, stream);

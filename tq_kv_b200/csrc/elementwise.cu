@@ -384,7 +384,7 @@ TQ_API int tq_swiglu(const void* gu, int in_dtype, void* out, int out_dtype, int
     if (total == 0) return 0;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > (size_t)tq_sm_count() * 32) blocks = (size_t)tq_sm_count() * 32;
 #define TQ_LAUNCH(TI, TO) \
     swiglu_kernel<TI, TO><<<(int)blocks, threads, 0, stream>>>((const TI*)gu, (TO*)out, I, total)
     if (in_dtype == TQ_F32 && out_dtype == TQ_F32) TQ_LAUNCH(float, float);
@@ -410,7 +410,7 @@ TQ_API int tq_add_into(float* acc, const void* x, int in_dtype, size_t total, cu
     if (total == 0) return 0;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > (size_t)tq_sm_count() * 32) blocks = (size_t)tq_sm_count() * 32;
     if (in_dtype == TQ_F32) add_into_kernel<float><<<(int)blocks, threads, 0, stream>>>(acc, (const float*)x, total);
     else if (in_dtype == TQ_BF16) add_into_kernel<bf16><<<(int)blocks, threads, 0, stream>>>(acc, (const bf16*)x, total);
     else return (int)cudaErrorInvalidValue;

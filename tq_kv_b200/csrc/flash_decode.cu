@@ -276,21 +276,24 @@ template <int HD>
 static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, const int* table, int table_width,
                                int ring_pages, const int* tok_pos, const int* tok_seq, int window, float scale,
                                bf16* out, float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int n_splits,
-                               cudaStream_t stream) {
+                               int pdl_family, cudaStream_t stream) {
     constexpr int ROW = HD * 2 + 16;
     constexpr int FD_CHUNK = HD <= 64 ? 32 : 16;
     constexpr size_t stage_bytes = (size_t)FD_WARPS * FD_STAGES * 2 * FD_CHUNK * ROW;
     constexpr size_t merge_bytes = (size_t)FD_WARPS * 16 * (HD + 2) * sizeof(float);
     constexpr size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};         // per device: the attribute belongs to the device's copy of the kernel
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<HD, FD_CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured[dev] = true;
     }
     const dim3 grid(n_tokens, nkv, n_splits);
-    return tq_launch_pdl(TQ_PDL_FLASH_DECODE, flash_decode_kernel<HD, FD_CHUNK>, grid, dim3(FD_WARPS * 32), smem, stream, q, kp, vp, table,
+    return tq_launch_pdl(pdl_family, flash_decode_kernel<HD, FD_CHUNK>, grid, dim3(FD_WARPS * 32), smem, stream, q, kp, vp, table,
                          table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out, part_acc,
                          part_ml, nh, nkv, n_splits);
 }
@@ -298,10 +301,17 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
 // Returns cudaErrorNotSupported (801) for shapes outside this kernel's reach
 // (head_dim not in {32, 64, 96, 128}, more than 16 q heads per key/value
 // head, pages of another size); the caller then uses the general kernel.
-TQ_API int tq_flash_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
-                           int table_width, int ring_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
-                           int window, float scale, void* out, float* part_acc, float* part_ml, int n_tokens, int nh,
-                           int nkv, int hd, int n_splits, cudaStream_t stream) {
+//
+// `early_start`: launch the kernel so that it may begin while its predecessor in the stream still runs
+// (programmatic dependent launch).  Its blocks then read the positions, the block table and every key older than
+// the token's own before the predecessor has ended; that is right only if the predecessor writes nothing but q
+// and each token's newest key, as the kernels of a decode step do.  With 0 the kernel starts after everything
+// before it in the stream has completed, whatever that was.
+static int flash_decode_launch(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                               int table_width, int ring_pages, int page_tokens, const int* tok_pos,
+                               const int* tok_seq, int window, float scale, void* out, float* part_acc,
+                               float* part_ml, int n_tokens, int nh, int nkv, int hd, int n_splits, int early_start,
+                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv || nh / nkv > 16 || page_tokens != FD_PAGE || nkv > 65535 || n_splits > 65535)
         return (int)cudaErrorNotSupported;
@@ -310,7 +320,8 @@ TQ_API int tq_flash_decode(const void* q, const void* k_pages, const void* v_pag
     case H:                                                                                                       \
         return launch_flash_decode<H>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table,   \
                                       table_width, ring_pages, tok_pos, tok_seq, window, scale, (bf16*)out,      \
-                                      part_acc, part_ml, n_tokens, nh, nkv, n_splits, stream)
+                                      part_acc, part_ml, n_tokens, nh, nkv, n_splits,                \
+                                      early_start ? TQ_PDL_FLASH_DECODE : 0, stream)
     switch (hd) {
         TQ_FD(32);
         TQ_FD(64);
@@ -319,4 +330,12 @@ TQ_API int tq_flash_decode(const void* q, const void* k_pages, const void* v_pag
         default: return (int)cudaErrorNotSupported;
     }
 #undef TQ_FD
+}
+
+TQ_API int tq_flash_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                           int table_width, int ring_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
+                           int window, float scale, void* out, float* part_acc, float* part_ml, int n_tokens, int nh,
+                           int nkv, int hd, int n_splits, cudaStream_t stream) {
+    return flash_decode_launch(q, k_pages, v_pages, block_table, table_width, ring_pages, page_tokens, tok_pos, tok_seq,
+                               window, scale, out, part_acc, part_ml, n_tokens, nh, nkv, hd, n_splits, 1, stream);
 }

@@ -74,9 +74,11 @@ int tq_flash_decode_static(const void* q, const void* k_pages, const void* v_pag
         part_acc = base;
         part_ml = base + rows * head_dim;
     }
-    int st = tq_flash_decode(q, k_pages, v_pages, block_table, table_width, ring_pages, page_tokens, tok_pos, tok_seq,
-                             window, scale, out, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, n_splits,
-                             stream);
+    // Without an early start: whatever the caller ran before in this stream (a kernel that writes the positions,
+    // the table or many keys) has completed before the first block reads anything.
+    int st = flash_decode_launch(q, k_pages, v_pages, block_table, table_width, ring_pages, page_tokens, tok_pos,
+                                 tok_seq, window, scale, out, part_acc, part_ml, n_tokens, n_heads, n_kv_heads,
+                                 head_dim, n_splits, 0, stream);
     if (st == (int)cudaErrorNotSupported) {
         snprintf(g_error, sizeof g_error,
                  "unsupported shape: head_dim %d (32, 64, 96 or 128), %d q heads per key/value head (at most 16), "

@@ -17,6 +17,13 @@
  *
  * The first call on a device looks the array's device address up (no
  * allocation) and keeps it; make that first call outside any stream capture.
+ * Two host threads that make their first calls on one device at the same
+ * moment both look it up and store the same answer.
+ *
+ * The kernels start only after everything that precedes them in the stream
+ * has completed (no early start under a predecessor's tail, unlike the same
+ * kernels inside this library's own decode step), so the caller's earlier
+ * kernels may write any of the inputs: positions, table, keys, values, q.
  *
  * All calls share the one array.  Nothing in it has to start at zero: every
  * entry that the merge step reads is written by the same call first.  But two

@@ -601,16 +601,7 @@ static int tc_last_round_parts(int n_tiles, int sms, int K, double* gain) {
     return parts;
 }
 
-static int tc_sm_count() {
-    static int sm_count = 0;
-    if (!sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 1;
-    }
-    return sm_count;
-}
+static int tc_sm_count() { return tq_sm_count(); }
 
 template <int EPI, typename TO>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const float* bias, int M, int N,

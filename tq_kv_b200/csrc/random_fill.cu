@@ -84,7 +84,7 @@ TQ_API int tq_random_fill(void* out, int out_dtype, size_t n, unsigned long long
     if (n == 0) return 0;
     const int threads = 256;
     size_t blocks = (n + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > (size_t)tq_sm_count() * 16) blocks = (size_t)tq_sm_count() * 16;
     if (out_dtype == TQ_F32)
         random_fill_kernel<float><<<(int)blocks, threads, 0, stream>>>((float*)out, n, key, std, offset);
     else if (out_dtype == TQ_BF16)

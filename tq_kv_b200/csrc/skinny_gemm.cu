@@ -187,7 +187,7 @@ static int launch_skinny(const bf16* X, const bf16* W, const float* bias, void* 
     const int tiles = (N + COLS - 1) / COLS;
     // split K over a cluster while the grid is small and every warp keeps a few k-blocks
     int ranks = 1;
-    while (ranks < 8 && tiles * ranks < 4 * 148 && (K >> 5) / (SK_WARPS * ranks * 2) >= 4) ranks *= 2;
+    while (ranks < 8 && tiles * ranks < 4 * tq_sm_count() && (K >> 5) / (SK_WARPS * ranks * 2) >= 4) ranks *= 2;
     constexpr size_t smem = sizeof(float) * SK_WARPS * TW * 16 * (8 * NT + 1);
     static bool configured = false;          // per template instance
     if (smem > 48 * 1024 && !configured) {

@@ -1,7 +1,12 @@
 """Arrangement of a layer's parts.  `prenorm_residual` is the reference's
 (src/models/turbo_generic.rs:1959-1981): h += mixer(norm1(h));
 h += feed_forward(norm2(h)), with the sums done in float32 on the residual
-stream."""
+stream.
+
+A block kind is a class built from a `LayerSpec` with `parts()` (every part
+it holds, for weights and binding), `mixer` (the one part that may ask for a
+cache or state) and `forward(h, ctx)`.  It takes the parts it arranges from
+the layer by name (`spec.part("mixer")`, or any name of `extra_parts`)."""
 from __future__ import annotations
 
 from .. import kernels
@@ -13,10 +18,10 @@ from .registry import make_part
 class PrenormResidualBlock:
     def __init__(self, spec: LayerSpec):
         self.spec = spec
-        self.mixer_norm = make_part(spec.mixer_norm)
-        self.mixer = make_part(spec.mixer)
-        self.feed_forward_norm = make_part(spec.feed_forward_norm)
-        self.feed_forward = make_part(spec.feed_forward)
+        self.mixer_norm = make_part(spec.part("mixer_norm"))
+        self.mixer = make_part(spec.part("mixer"))
+        self.feed_forward_norm = make_part(spec.part("feed_forward_norm"))
+        self.feed_forward = make_part(spec.part("feed_forward"))
 
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]

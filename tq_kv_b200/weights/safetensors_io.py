@@ -102,22 +102,53 @@ class SafetensorsFile:
         self._f.close()
 
 
+INDEX_NAME = "model.safetensors.index.json"
+
+
 def open_model_files(folder: str) -> tuple[list[SafetensorsFile], dict[str, SafetensorsFile]]:
     """All safetensors files of a model folder and the map from tensor name to
-    the file that holds it.  A name found in two files is an error."""
+    the file that holds it.  A name found in two files is an error.  If the
+    folder has a `model.safetensors.index.json`, its `weight_map` decides:
+    only the files it names are opened (a stray file beside them is not
+    read), and a tensor that the map places in a file that does not hold it is
+    an error.  (The reference scans the folder and ignores the index:
+    src/models/turbo_generic.rs:2038-2053.)"""
     try:
-        names = sorted(f for f in os.listdir(folder) if f.endswith(".safetensors"))
+        present = sorted(f for f in os.listdir(folder) if f.endswith(".safetensors"))
     except OSError as e:
         raise SafetensorsError(f"Cannot read model dir: {e}") from e
+    weight_map = None
+    index_path = os.path.join(folder, INDEX_NAME)
+    if os.path.isfile(index_path):
+        try:
+            with open(index_path) as f:
+                weight_map = json.load(f)["weight_map"]
+            if not isinstance(weight_map, dict):
+                raise TypeError("weight_map is no object")
+        except (OSError, ValueError, KeyError, TypeError) as e:
+            raise SafetensorsError(f"Invalid {INDEX_NAME}: {e}") from e
+        names = sorted(set(weight_map.values()))
+        lost = [n for n in names if n not in present]
+        if lost:
+            raise SafetensorsError(f"{INDEX_NAME} names files that are not in {folder}: {', '.join(lost)}")
+    else:
+        names = present
     if not names:
         raise SafetensorsError(f"No .safetensors files found in {folder}")
     files = [SafetensorsFile(os.path.join(folder, n)) for n in names]
     where: dict[str, SafetensorsFile] = {}
     for f in files:
         for name in f.entries:
+            if weight_map is not None and weight_map.get(name) != os.path.basename(f.path):
+                continue                      # the index places this tensor elsewhere (or nowhere)
             if name in where:
                 raise SafetensorsError(f"tensor '{name}' is stored twice: in {where[name].path} and in {f.path}")
             where[name] = f
+    if weight_map is not None:
+        wrong = sorted(n for n in weight_map if n not in where)
+        if wrong:
+            raise SafetensorsError(f"{INDEX_NAME} places tensors in files that do not hold them: "
+                                   + ", ".join(f"{n} -> {weight_map[n]}" for n in wrong))
     return files, where
 
 
