@@ -236,6 +236,65 @@ def test_decode_gemm_tc(M, N, K):
     kernels.check_tc_status()
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K,big", [(37, 64, False), (100, 96, False), (512, 3584, False), (200, 1000, True),
+                                     (4608, 3584, True), (129, 7168, True), (640, 8, True)])
+def test_decode_products_with_the_norm_folded_in(M, N, K, big, monkeypatch):
+    """kernels.linear() given a pending RMS norm instead of activations: the mma.sync kernel (small weights) and
+    the tcgen05 kernel (large weights, or K no multiple of 32) read the float32 rows, multiply with the norm's
+    weights while they build their operand and scale their sums by each row's 1/rms.  The reference rounds
+    h * g to bfloat16 as the kernels do, so the bound is that of float32 summation alone; plain, accumulating
+    and gated epilogues; then against the norm run as a kernel of its own."""
+    from tq_kv_b200 import kernels
+    if big:
+        monkeypatch.setattr(kernels.gemm, "TC_DECODE_MIN_WEIGHT_BYTES", 0)       # send it to the tcgen05 kernel
+    monkeypatch.setattr(kernels.gemm, "FUSE_NORM", True)                         # wherever a kernel can
+    eps = 1e-5
+    h, g = rnd(M, K, seed=7, scale=3.0), 1.0 + rnd(K, seed=8, scale=0.2)
+    w, bias = rnd(N, K, dtype=torch.bfloat16, seed=1), rnd(N, seed=2)
+    x = (h * g).to(torch.bfloat16).double()
+    rms = torch.sqrt((h.double() ** 2).mean(-1, keepdim=True) + eps)
+    want = (x @ w.double().T) / rms
+    tol = 1e-5 * math.sqrt(max(K, 64) / 64)
+    n0 = kernels.launches[0]
+    out = kernels.linear(kernels.PendingNorm(h, g, eps, torch.bfloat16), w, bias=bias, out_dtype=torch.float32)
+    assert kernels.launches[0] - n0 == 1                                        # one kernel: no norm of its own
+    close(out, want + bias.double(), tol, "folded norm")
+    res = rnd(M, N, seed=3)
+    base = res.clone()
+    kernels.linear(kernels.PendingNorm(h, g, eps, torch.bfloat16), w, out=res, accumulate=True)
+    close(res, base.double() + want, tol, "folded norm, accumulate")
+    w2, b2 = rnd(2 * N, K, dtype=torch.bfloat16, seed=4, scale=2.0 / math.sqrt(K)), rnd(2 * N, seed=5)
+    y = (x @ w2.double().T) / rms + b2.double()
+    out = kernels.linear(kernels.PendingNorm(h, g, eps, torch.bfloat16), w2, bias=b2, swiglu=True,
+                         out_dtype=torch.float32)
+    close(out, torch.nn.functional.silu(y[:, :N]) * y[:, N:], tol, "folded norm, gated")
+    out = kernels.linear(kernels.PendingNorm(h, g, eps, torch.bfloat16), w2, swiglu=True, out_dtype=torch.bfloat16)
+    y = (x @ w2.double().T) / rms
+    close(out, torch.nn.functional.silu(y[:, :N]) * y[:, N:], 4e-3, "folded norm, gated, bf16 out")
+    # the same through the norm's own kernel: rounding of the normed rows to bfloat16 is the only difference
+    monkeypatch.setattr(kernels.gemm, "FUSE_NORM", False)
+    n0 = kernels.launches[0]
+    apart = kernels.linear(kernels.PendingNorm(h, g, eps, torch.bfloat16), w, bias=bias, out_dtype=torch.float32)
+    assert kernels.launches[0] - n0 >= 2
+    close(apart, want + bias.double(), 8e-3, "norm as a kernel of its own")
+    kernels.check_tc_status()
+
+
+def test_a_pending_norm_runs_as_its_own_kernel_where_no_product_takes_it():
+    """More rows than the decode products fold a norm for, float32 weights, a float32 result dtype: the norm's
+    kernel runs first and the product follows; the result is the same either way."""
+    from tq_kv_b200 import kernels
+    eps = 1e-6
+    for M, wdt, odt in ((17, torch.bfloat16, torch.bfloat16), (200, torch.bfloat16, torch.bfloat16),
+                        (4, torch.float32, torch.float32)):
+        h, g = rnd(M, 256, seed=9, scale=2.0), 1.0 + rnd(256, seed=10, scale=0.1)
+        w = rnd(300, 256, dtype=wdt, seed=11, scale=0.1)
+        x = (h.double() / torch.sqrt((h.double() ** 2).mean(-1, keepdim=True) + eps)) * g.double()
+        out = kernels.linear(kernels.PendingNorm(h, g, eps, odt), w, out_dtype=torch.float32)
+        close(out, x @ w.double().T, 8e-3 if odt == torch.bfloat16 else 1e-5, f"pending norm, {M} rows")
+
+
 @pytest.mark.parametrize("mode", [1, 2])
 def test_gemm_tc_accumulate_with_a_short_last_round(mode):
     """More tiles than SMs with a remainder: the residual product cuts the last round's tiles along K and the

@@ -75,11 +75,25 @@ __device__ __forceinline__ void dg_ld32(uint32_t taddr, float* v) {
 // MP: padded batch (32 or 64) = columns of the accumulator.
 // DG_STAGES: 4 (96 KB per block: two blocks fit an SM, one's epilogue runs under the other's loads).  Inside the
 // decode step five stages were slower (200 KB an SM leave the next kernel no room to set itself up), eight too.
-template <int MP, bool SWIGLU, typename TO, int DG_STAGES, bool REDUCE>
+//
+// NORM (cluster form, up to 16 batch rows): the activations are the float32 residual stream H [M, K] and the
+// weights G [K] of an RMS norm (src/models/turbo_generic.rs:41-51) instead of bfloat16 rows.  The four warps
+// that later run the epilogue build each stage's X tile themselves: every thread fetches eight values of one
+// row through a small cp.async ring of its own (four stages ahead of the tile it writes), multiplies them with
+// g, rounds to bfloat16 and stores them where the 128-byte swizzle of the tile wants them; the squares are
+// summed on the way, each block over its share of K, and the shares meet with the partial products in the
+// cluster's exchange, where every output is scaled by 1 / sqrt(mean(h^2) + eps) of its batch row.  So the norm
+// needs no kernel and no trip through memory of its own.
+#define DG_NORM_ROWS 16
+#define DG_HRING 4
+template <int MP, bool SWIGLU, typename TO, int DG_STAGES, bool REDUCE, bool NORM = false>
 __global__ void __launch_bounds__(DG_THREADS, 2)
 decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       const __grid_constant__ CUtensorMap map_y, const float* __restrict__ bias, TO* __restrict__ Y,
-                      int M, int N, int K, int ldy, int accumulate, int k_splits, int* __restrict__ status) {
+                      int M, int N, int K, int ldy, int accumulate, int k_splits, int* __restrict__ status,
+                      const float* __restrict__ H = nullptr, int ldh = 0, const float* __restrict__ G = nullptr,
+                      float eps = 0.f) {
+    static_assert(!NORM || (!REDUCE && MP == 32), "the folded norm runs in the cluster form with up to 16 rows");
     constexpr int X_BYTES = MP * DG_BK * 2;
     constexpr int STAGE_BYTES = DG_W_BYTES + X_BYTES;
     constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
@@ -94,6 +108,8 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     uint64_t* acc_full = bars + 2 * DG_STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * DG_STAGES + 1);
     volatile uint32_t* failed = tmem_slot + 1;
+    float* ss_part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 128);   // NORM: [16] sums of squares
+    unsigned char* hring = reinterpret_cast<unsigned char*>(bars) + 256;                       // NORM: [DG_HRING][128][32 B]
 
     cg::cluster_group cluster = cg::this_cluster();
     // shares of K: the blocks of a cluster, or (REDUCE) k_splits independent blocks in a row of the grid
@@ -108,7 +124,7 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < DG_STAGES; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(dg_smem(&full[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(dg_smem(&full[s])), "r"(NORM ? 2u : 1u));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(dg_smem(&empty[s])));
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(dg_smem(acc_full)));
@@ -135,8 +151,8 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const int s = i % DG_STAGES;
             const uint32_t fb = dg_smem(&full[s]);
             const uint32_t w_dst = dg_smem(tiles + s * STAGE_BYTES);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(fb), "r"((uint32_t)STAGE_BYTES)
-                         : "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
+                         ::"r"(fb), "r"((uint32_t)(NORM ? DG_W_BYTES : STAGE_BYTES)) : "memory");
             const int kc = (k_lo + i) * DG_BK;
             if (SWIGLU) {
                 dg_tma(w_dst, &map_w, kc, n0, fb);                          // 64 gate rows
@@ -153,12 +169,13 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         for (int i = 0; i < ahead; ++i) load_w(i);
         pdl_wait();
         pdl_launch();
-        for (int i = 0; i < ahead; ++i) load_x(i);
+        if (!NORM)
+            for (int i = 0; i < ahead; ++i) load_x(i);
         for (int i = ahead; i < k_iters; ++i) {
             const int s = i % DG_STAGES;
             if (!dg_wait(dg_smem(&empty[s]), ((i / DG_STAGES) & 1) ^ 1)) { *failed = 1; break; }
             load_w(i);
-            load_x(i);
+            if (!NORM) load_x(i);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: D[128 x MP] (+)= W_tile[128 x 64] · X_tile[MP x 64]^T ----
@@ -184,6 +201,89 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         }
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                      ::"r"(dg_smem(acc_full)) : "memory");
+    }
+    if (NORM && warp >= 2) {
+        // ---- the X tiles from the residual stream (see NORM above); these threads have passed pdl_wait() ----
+        const int t = threadIdx.x - 64;                    // 0..127: row t / 8 of the tile, 16-byte piece t % 8
+        const int row = t >> 3, piece = t & 7;
+        const bool row_on = row < M;
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        for (int s = 0; s < DG_STAGES; ++s)                // rows from M on stay zero in every stage
+            for (int e = t; e < X_BYTES / 16; e += 128)
+                *reinterpret_cast<uint4*>(tiles + s * STAGE_BYTES + DG_W_BYTES + e * 16) = zero;
+        const float* hrow = H + (size_t)(row_on ? row : 0) * ldh;
+        unsigned char* mine = hring + t * 32;
+        auto fetch = [&](int i) {                          // one group per turn, empty or not
+            const int k = (k_lo + i) * DG_BK + piece * 8;
+            if (row_on && i < k_iters && k < K) {
+                const uint32_t dst = dg_smem(mine + (i % DG_HRING) * (128 * 32));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(hrow + k) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + 16), "l"(hrow + k + 4) : "memory");
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        };
+#pragma unroll
+        for (int i = 0; i < DG_HRING - 1; ++i) fetch(i);
+        float ss = 0.f;
+        // the norm's weights for the next DG_HRING tiles wait in registers: they do not depend on the kernel
+        // before and are asked for that many turns ahead of their use
+        float4 gq[DG_HRING][2];
+        auto fetch_g = [&](int i, float4* dst) {
+            const int k = (k_lo + i) * DG_BK + piece * 8;
+            if (i < k_iters && k < K) {
+                dst[0] = *reinterpret_cast<const float4*>(G + k);
+                dst[1] = *reinterpret_cast<const float4*>(G + k + 4);
+            } else {
+                dst[0] = dst[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        };
+#pragma unroll
+        for (int j = 0; j < DG_HRING; ++j) fetch_g(j, gq[j]);
+        bool stop = false;
+        for (int i0 = 0; i0 < k_iters && !stop; i0 += DG_HRING) {
+#pragma unroll
+            for (int j = 0; j < DG_HRING; ++j) {
+                const int i = i0 + j;
+                if (i >= k_iters || stop) break;
+                const int s = i % DG_STAGES;
+                const int k = (k_lo + i) * DG_BK + piece * 8;
+                const bool on = row_on && k < K;
+                const float4 g0 = gq[j][0], g1 = gq[j][1];
+                fetch(i + DG_HRING - 1);
+                asm volatile("cp.async.wait_group %0;\n" ::"n"(DG_HRING - 1) : "memory");      // this turn's values are here
+                const bool stage_free = i < DG_STAGES || dg_wait(dg_smem(&empty[s]), ((i / DG_STAGES) & 1) ^ 1);
+                uint4 packed = zero;
+                if (on) {
+                    const float4 h0 = *reinterpret_cast<const float4*>(mine + (i % DG_HRING) * (128 * 32));
+                    const float4 h1 = *reinterpret_cast<const float4*>(mine + (i % DG_HRING) * (128 * 32) + 16);
+                    ss = fmaf(h0.x, h0.x, ss); ss = fmaf(h0.y, h0.y, ss); ss = fmaf(h0.z, h0.z, ss); ss = fmaf(h0.w, h0.w, ss);
+                    ss = fmaf(h1.x, h1.x, ss); ss = fmaf(h1.y, h1.y, ss); ss = fmaf(h1.z, h1.z, ss); ss = fmaf(h1.w, h1.w, ss);
+                    __nv_bfloat162 a = __floats2bfloat162_rn(h0.x * g0.x, h0.y * g0.y), b = __floats2bfloat162_rn(h0.z * g0.z, h0.w * g0.w);
+                    __nv_bfloat162 c = __floats2bfloat162_rn(h1.x * g1.x, h1.y * g1.y), d = __floats2bfloat162_rn(h1.z * g1.z, h1.w * g1.w);
+                    packed = make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b),
+                                        *reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+                }
+                fetch_g(i + DG_HRING, gq[j]);              // this slot's next use is DG_HRING turns away
+                if (row_on && stage_free)                  // K-major tile, 128-byte swizzle: piece ^ (row % 8)
+                    *reinterpret_cast<uint4*>(tiles + s * STAGE_BYTES + DG_W_BYTES + row * 128 + ((piece ^ (row & 7)) << 4)) = packed;
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                // the 128 threads meet once per tile and agree on whether every one of them got the stage in time
+                uint32_t all_free;
+                asm volatile(
+                    "{\n\t.reg .pred p, q;\n\t"
+                    "setp.ne.u32 p, %1, 0;\n\t"
+                    "bar.red.and.pred q, 1, 128, p;\n\t"
+                    "selp.u32 %0, 1, 0, q;\n\t}\n"
+                    : "=r"(all_free) : "r"((uint32_t)stage_free) : "memory");
+                if (!all_free) { *failed = 1; stop = true; break; }
+                if (t == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(dg_smem(&full[s])) : "memory");
+            }
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+        if (piece == 0) ss_part[row] = ss;
     }
     __syncwarp();
 
@@ -260,6 +360,9 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const float* peers[8];
 #pragma unroll
         for (int p = 0; p < 8; ++p) peers[p] = p < n_ranks ? cluster.map_shared_rank(red, p) : red;
+        const float* peer_ss[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p) peer_ss[p] = (NORM && p < n_ranks) ? cluster.map_shared_rank(ss_part, p) : ss_part;
         const int runs = (OUT_COLS / 32) * M;
         const int step = n_ranks * (DG_THREADS / 32);
         // four runs per turn: all their (remote) reads are in flight before the first sum
@@ -286,6 +389,14 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
                 for (int p = 1; p < 8; ++p) { v += pv[u][p]; w += pu[u][p]; }
                 if (col >= N) continue;
+                if (NORM) {
+                    float q2 = peer_ss[0][m];
+#pragma unroll
+                    for (int p = 1; p < 8; ++p) q2 += p < n_ranks ? peer_ss[p][m] : 0.f;
+                    const float rms = sqrtf(q2 / (float)K + eps);
+                    v /= rms;
+                    if (SWIGLU) w /= rms;
+                }
                 if (bias) { v += bias[col]; if (SWIGLU) w += bias[col + N]; }
                 if (SWIGLU) v = (v / (1.f + expf(-v))) * w;
                 TO* y = Y + (size_t)m * ldy + col;
@@ -346,18 +457,20 @@ static int dg_launch_reduce(const CUtensorMap& mw, const CUtensorMap& mx, const 
     }
     const int tiles = (N + DG_ROWS - 1) / DG_ROWS;
     return tq_launch_pdl(TQ_PDL_DECODE_GEMM, decode_gemm_tc_kernel<MP, false, float, STAGES, true>, dim3(tiles * splits), dim3(DG_THREADS),
-                         SMEM, stream, mw, mx, my, bias, Y, M, N, K, ldy, 1, splits, status);
+                         SMEM, stream, mw, mx, my, bias, Y, M, N, K, ldy, 1, splits, status, (const float*)nullptr, 0,
+                         (const float*)nullptr, 0.f);
 }
 
-template <int MP, bool SWIGLU, typename TO, int DG_STAGES>
+template <int MP, bool SWIGLU, typename TO, int DG_STAGES, bool NORM = false>
 static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* Y, int M, int N, int K,
-                       int ldy, int accumulate, int* status, int ranks, cudaStream_t stream) {
+                       int ldy, int accumulate, int* status, int ranks, cudaStream_t stream, const float* H = nullptr,
+                       int ldh = 0, const float* G = nullptr, float eps = 0.f) {
     constexpr int STAGE_BYTES = DG_W_BYTES + MP * DG_BK * 2;
-    constexpr int SMEM = DG_STAGES * STAGE_BYTES + 1024 + 256;
+    constexpr int SMEM = DG_STAGES * STAGE_BYTES + 1024 + 256 + (NORM ? DG_HRING * 128 * 32 : 0);
     static_assert(DG_ROWS * (MP + 1) * 4 <= DG_STAGES * STAGE_BYTES, "partial sums must fit in the stages");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false>,
+        cudaError_t e = cudaFuncSetAttribute(decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false, NORM>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -378,9 +491,9 @@ static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float
     attr[1].val.programmaticStreamSerializationAllowed = tq_pdl_enabled(TQ_PDL_DECODE_GEMM) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false>, mw, mx,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false, NORM>, mw, mx,
                                        mw /* no map of Y in this form */, bias, (TO*)Y, M, N, K, ldy, accumulate, 1,
-                                       status);
+                                       status, H, ldh, G, eps);
     if (e != cudaSuccess) return (int)e;
     return tq_launch_status();
 }
@@ -440,5 +553,35 @@ TQ_API int tq_decode_gemm_tc(const void* X, const void* W, const float* bias, vo
         if (!swiglu && y_dtype == TQ_F32) TQ_DG(64, false, float);
     }
 #undef TQ_DG
+    return (int)cudaErrorInvalidValue;
+}
+
+// The same product with an RMS norm folded in (see NORM at the kernel): H [M <= 16, K] is the float32 residual
+// stream (row stride ldh, a multiple of 4; base 16-byte aligned), G [K] the norm's float32 weights.  K is split
+// over a thread-block cluster as in the plain form.
+TQ_API int tq_decode_gemm_tc_norm(const float* H, const float* G, float eps, const void* W, const float* bias, void* Y,
+                                  int y_dtype, int M, int N, int K, int ldh, int ldw, int ldy, int accumulate,
+                                  int swiglu, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > DG_NORM_ROWS || K <= 0 || (K & 7) || (ldh & 3) || (ldw & 7) || !G || !H) return (int)cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(H) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+        (reinterpret_cast<uintptr_t>(G) & 15))
+        return (int)cudaErrorInvalidValue;
+    if (accumulate && y_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    CUtensorMap mw;
+    int st = dg_make_map(&mw, W, swiglu ? 2ull * N : (uint64_t)N, (uint64_t)K, (uint64_t)ldw,
+                         swiglu ? DG_ROWS / 2 : DG_ROWS);
+    if (st) return st;
+    const int out_cols = swiglu ? DG_ROWS / 2 : DG_ROWS;
+    const int tiles = (N + out_cols - 1) / out_cols, k_total = (K + DG_BK - 1) / DG_BK;
+    int ranks = 1;
+    while (ranks < 8 && tiles * ranks < tq_sm_count() && k_total / (ranks * 2) >= 4) ranks *= 2;
+#define TQ_DGN(S, T) \
+    return dg_launch_s<32, S, T, 4, true>(mw, mw, bias, Y, M, N, K, ldy, accumulate, status, ranks, stream, H, ldh, G, eps)
+    if (swiglu && y_dtype == TQ_BF16) TQ_DGN(true, bf16);
+    if (swiglu && y_dtype == TQ_F32) TQ_DGN(true, float);
+    if (!swiglu && y_dtype == TQ_BF16) TQ_DGN(false, bf16);
+    if (!swiglu && y_dtype == TQ_F32) TQ_DGN(false, float);
+#undef TQ_DGN
     return (int)cudaErrorInvalidValue;
 }

@@ -151,6 +151,10 @@ _SIGNATURES = {
                      c_int, c_int, c_int, c_int, c_void_p],
     "tq_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                        c_int, c_int, c_void_p],
+    "tq_skinny_gemm_norm": [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                            c_int, c_int, c_int, c_int, c_void_p],
+    "tq_decode_gemm_tc_norm": [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "tq_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_void_p, c_void_p],
     "tq_gemm_tc_mode": [c_int],

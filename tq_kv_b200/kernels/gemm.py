@@ -19,6 +19,7 @@
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -26,6 +27,42 @@ import torch
 from . import elementwise
 from ._lib import KernelError, check, check_tc_status, core, dtype_code, need_contiguous, ptr, stream, tc_status_word
 
+class PendingNorm:
+    """An RMS norm that has not run yet: the float32 rows `h`, the norm's
+    float32 weights and eps, and the dtype its result would have.  `linear()`
+    takes it in place of activations and, where a decode kernel can, folds
+    the norm into the product (the kernel reads h, multiplies with the
+    weights while it builds its operand and scales its sums by each row's
+    1 / sqrt(mean(h^2) + eps)); otherwise `materialize()` runs the norm's own
+    kernel.  (src/models/turbo_generic.rs:41-51 is the norm.)"""
+
+    def __init__(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype):
+        self.h, self.weight, self.eps, self.out_dtype = h, weight, float(eps), out_dtype
+        self._done: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    @property
+    def device(self):
+        return self.h.device
+
+    @property
+    def dtype(self):
+        return self.out_dtype
+
+    def materialize(self) -> torch.Tensor:
+        if self._done is None:
+            out = torch.empty(self.h.shape, dtype=self.out_dtype, device=self.h.device)
+            self._done = elementwise.rmsnorm(self.h, self.weight, self.eps, out)
+        return self._done
+
+
+# Fold a pending norm into the decode products: True wherever a kernel can, False nowhere, "auto" where it was
+# measured to pay (see _fused_norm).  TQ_FUSE_NORM=1 / 0 set True / False.
+FUSE_NORM = {"1": True, "0": False}.get(os.environ.get("TQ_FUSE_NORM", ""), "auto")
+FUSED_NORM_MAX_ROWS = 16
 ROW_KERNEL_MAX_ROWS = 16
 SKINNY_MAX_ROWS = 64
 TC_DECODE_MIN_WEIGHT_BYTES = 24 << 20      # see linear()
@@ -77,6 +114,34 @@ def decode_gemm_tc(x, w, out, bias=None, accumulate=False, swiglu=False):
     return out
 
 
+def _fused_norm(x: "PendingNorm", w, out, bias, accumulate, swiglu) -> bool:
+    """Runs out (=, +=) norm(h) . w^T with the norm folded into a decode product; False if none takes it."""
+    h, g = x.h, x.weight
+    M, K = h.shape
+    big = w.numel() * 2 >= TC_DECODE_MIN_WEIGHT_BYTES or K % 32 != 0          # the tcgen05 kernel's case
+    # Measured inside whole decode steps: the tcgen05 kernel gains from the folded norm where it runs in its
+    # cluster form anyway (gated products: 7B shape -0.8 % of a step) and loses where the norm costs it the
+    # form with independent shares of K (float32 results: +8 %); the mma.sync kernel gains for plain products
+    # (0.5B shape -1.5 %) and loses for gated ones, whose registers are scarce (+2 %).
+    if FUSE_NORM == "auto" and big != bool(swiglu):
+        return False
+    if not (FUSE_NORM and USE_TCGEN05 and x.out_dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and h.dtype == torch.float32 and g.dtype == torch.float32 and 0 < M <= FUSED_NORM_MAX_ROWS
+            and h.stride(1) == 1 and h.stride(0) % 4 == 0 and h.data_ptr() % 16 == 0 and g.data_ptr() % 16 == 0
+            and g.is_contiguous() and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and K % 8 == 0
+            and out.dtype in (torch.float32, torch.bfloat16) and (not accumulate or out.dtype == torch.float32)
+            and (not swiglu or w.shape[0] % 2 == 0)):
+        return False
+    N = out.shape[1]
+    args = (ptr(h), ptr(g), x.eps, ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, h.stride(0), w.stride(0),
+            out.stride(0), int(accumulate), int(swiglu))
+    if big:
+        check(core().tq_decode_gemm_tc_norm(*args, ptr(tc_status_word(h.device)), stream()), "decode_gemm_tc_norm")
+    else:
+        check(core().tq_skinny_gemm_norm(*args, stream()), "skinny_gemm_norm")
+    return True
+
+
 def _tc_ok(x, w, out, swiglu) -> bool:
     return (USE_TCGEN05 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
@@ -117,9 +182,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
     y = silu(x · gate^T) * (x · up^T); with `accumulate`, `out` (float32) gets
     y added to it.  x [M, K], w [N, K] (or [2N, K]); float32 accumulation
     throughout."""
-    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+    pending = x if isinstance(x, PendingNorm) else None
+    if len(x.shape) != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise KernelError(f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not multiply")
-    if x.stride(1) != 1 or w.stride(1) != 1:
+    if (pending is None and x.stride(1) != 1) or w.stride(1) != 1:
         raise KernelError("linear: operands must be contiguous along the inner dimension")
     M, K = x.shape
     rows_w = w.shape[0]
@@ -130,13 +196,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
         if out is None or out.dtype != torch.float32:
             raise KernelError("linear: accumulate needs a float32 `out`")
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)      # (a pending norm has both too)
     if tuple(out.shape) != (M, N) or out.stride(1) != 1:
         raise KernelError(f"linear: out has shape {tuple(out.shape)}, expected {(M, N)}")
     if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != rows_w):
         raise KernelError("linear: bias must be float32 with one entry per weight row")
     if M == 0:
         return out
+    if pending is not None:
+        if _fused_norm(pending, w, out, bias, accumulate, swiglu):
+            return out
+        x = pending.materialize()
 
     # decoding: the TMA-fed tcgen05 kernel for batches over 16 rows and for weights from 24 MB on at any batch,
     # the mma.sync kernel for smaller weights at small batches.  The limit was set inside the whole decode step

@@ -22,6 +22,8 @@ from .registry import make_part
 
 
 class GQAttention(Mixer):
+    takes_pending_norm = True           # x goes to kernels.linear only
+
     def __init__(self, spec):
         super().__init__(spec)
         p = self.params

@@ -109,6 +109,9 @@ class Part:
     # it) sets this to False; the engine then launches that model's decode
     # steps kernel by kernel instead of replaying a captured CUDA graph.
     graph_capturable = True
+    # A mixer or feed-forward that hands its input to `kernels.linear` and reads it nowhere else may set this:
+    # the block then passes the norm before it as a `kernels.PendingNorm`, which the product can fold in.
+    takes_pending_norm = False
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

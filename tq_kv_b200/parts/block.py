@@ -28,9 +28,17 @@ class PrenormResidualBlock:
 
     def forward(self, h, ctx: StepContext) -> None:
         act = ctx.runtime.act_dtype
-        x = self.mixer_norm.forward(h, act)
+        x = self._normed(self.mixer_norm, self.mixer, h, act)
         kernels.mark("norms")
         self.mixer.forward(x, ctx, h)
-        x = self.feed_forward_norm.forward(h, act)
+        x = self._normed(self.feed_forward_norm, self.feed_forward, h, act)
         kernels.mark("norms")
         self.feed_forward.forward(x, ctx, h)
+
+    @staticmethod
+    def _normed(norm, consumer, h, act):
+        """The norm's result for `consumer` — left pending if the consumer only hands it to `kernels.linear`
+        (it says so with `takes_pending_norm`) and the norm can be deferred, so that the product may fold it in."""
+        if getattr(consumer, "takes_pending_norm", False) and hasattr(norm, "pending"):
+            return norm.pending(h, act)
+        return norm.forward(h, act)

@@ -10,6 +10,8 @@ from .base import FeedForward, Runtime, StepContext, WeightSpec
 
 
 class SwiGLU(FeedForward):
+    takes_pending_norm = True           # x goes to kernels.linear only
+
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden = int(self.params["hidden_size"])

@@ -27,3 +27,9 @@ class RMSNorm(Norm):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)
         return kernels.rmsnorm(x, self.weight, self.eps, out, rows)
+
+    def pending(self, x, out_dtype):
+        """The norm of all rows of x as a `kernels.PendingNorm`: a part that
+        feeds it to `kernels.linear` lets the product fold the norm in where
+        it can (else the norm runs then, as a kernel of its own)."""
+        return kernels.PendingNorm(x, self.weight, self.eps, out_dtype)
