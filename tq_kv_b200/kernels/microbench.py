@@ -3,6 +3,8 @@
   gemm        the many-row product (csrc/gemm_tc.cu) at one shape, on single SMs and on pairs, alternating
   decode-gemm the decode products (csrc/decode_gemm_tc.cu, csrc/skinny_gemm.cu) of a layer shape at one batch size
   attention   the prompt attention (csrc/flash_prefill_tc.cu) for prompts of given lengths
+  decode-attention  the attention of one decoded token per sequence over the paged cache
+              (csrc/flash_decode.cu and the merge of its splits) at one batch size and context
 
 Every timing loops over several copies of the large operand, so that it is read from memory and not from the L2,
 after three warm-up launches.  The numbers explain bench.py's; they are not a benchmark of the engine.
@@ -19,14 +21,27 @@ from ._lib import check_tc_status
 DEV = "cuda"
 
 
-def _time(fn, n_variants: int, reps: int) -> float:
-    """Mean microseconds of fn(i) over reps * n_variants launches."""
+def _time(fn, n_variants: int, reps: int, graph: bool = False) -> float:
+    """Mean microseconds of fn(i) over reps * n_variants launches.  With `graph`, one round over the variants
+    is captured into a CUDA graph and replayed, so that kernels of a few microseconds are not timed at the
+    pace of their launches from Python."""
     for i in range(min(3, n_variants)):
         fn(i)
     torch.cuda.synchronize()
+    g = None
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n_variants):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
+        if g is not None:
+            g.replay()
+            continue
         for i in range(n_variants):
             fn(i)
     e1.record()
@@ -88,6 +103,38 @@ def bench_attention(args) -> None:
     check_tc_status()
 
 
+def bench_decode_attention(args) -> None:
+    import importlib
+    att = importlib.import_module(__package__ + ".attention")   # (the package also exports a function of that name)
+    B, T, nh, nkv, hd = args.batch, args.context, args.heads, args.kv_heads, args.head_dim
+    width = -(-T // 64)
+    n_pages = B * width
+    copy_bytes = 2 * n_pages * nkv * 64 * hd * 2
+    n = max(2, min(16, int(600e6 // copy_bytes) + 1))
+    caches = [(torch.randn(n_pages, nkv, 64, hd, device=DEV, dtype=torch.bfloat16),
+               torch.randn(n_pages, nkv, 64, hd, device=DEV, dtype=torch.bfloat16)) for _ in range(n)]
+    table = torch.randperm(n_pages, device=DEV).reshape(B, width).to(torch.int32)
+    q = torch.randn(B, nh * hd, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = torch.full((B,), T - 1, dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    splits = att.plan_splits(B, nkv, args.plan_context or T, sms)
+    scratch = torch.empty(att.split_scratch_floats(B, nh, hd, splits), device=DEV) if splits > 1 else None
+
+    def run(i):
+        k, v = caches[i]
+        att.attention(q, out, n_heads=nh, n_kv_heads=nkv, head_dim=hd, tok_pos=pos, tok_seq=seq, cu_seqlens=cu,
+                      start_pos=pos, window=None, k_pages=k, v_pages=v, block_table=table, table_width=width,
+                      n_splits=splits, scratch=scratch)
+
+    us = _time(run, n, args.reps, graph=True)
+    read = B * T * nkv * hd * 2 * 2
+    print(f"decode attention, batch {B}, {T} cached tokens, {nh}/{nkv} heads of {hd}, {splits} splits: {us:8.1f} us, "
+          f"{read / 1e6:.1f} MB of keys and values, {read / us / 1e3:.0f} GB/s")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m tq_kv_b200.kernels.microbench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -117,6 +164,16 @@ def main(argv=None) -> int:
     a.add_argument("--lengths", type=int, nargs="+", default=[2048])
     a.add_argument("--reps", type=int, default=20)
     a.set_defaults(fn=bench_attention)
+    da = sub.add_parser("decode-attention")
+    da.add_argument("--batch", type=int, default=8)
+    da.add_argument("--context", type=int, default=3072)
+    da.add_argument("--plan-context", type=int, default=4096,
+                    help="the context the splits are planned for, as a replayed graph plans them (0: --context)")
+    da.add_argument("--heads", type=int, default=28)
+    da.add_argument("--kv-heads", type=int, default=4)
+    da.add_argument("--head-dim", type=int, default=128)
+    da.add_argument("--reps", type=int, default=20)
+    da.set_defaults(fn=bench_decode_attention)
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device")
