@@ -408,6 +408,16 @@ def test_qkv_rope_cache(cache_dtype, nh, nkv, hd, rot):
         close(vp[page, :, p % P], xv[i], tol, "v cache")
     written = sum(lens) * nkv * hd
     assert int((vp != 0).sum()) == written               # nothing else was touched
+    # the same with the input cleared behind the kernel: equal results, and zeros where qkv was
+    q2, kp2, vp2, keep = torch.empty_like(q), torch.zeros_like(kp), torch.zeros_like(vp), qkv.clone()
+    kernels.qkv_rope_cache(qkv, bias, cos.to(DEV), sin.to(DEV), tok_pos, tok_seq, new_lens, q2, n_heads=nh,
+                           n_kv_heads=nkv, head_dim=hd, rotary_dim=rot, k_pages=kp2, v_pages=vp2,
+                           block_table=table, table_width=4, ring_pages=0, page_tokens=P, clear_input=True)
+    assert float(qkv.abs().sum()) == 0.0 and float(keep.abs().sum()) > 0
+    tight = 0.0 if T < 128 else tol                      # under 128 tokens both calls ran the same kernel
+    close(q2, q, tight, "q, input cleared")
+    close(kp2, kp, tight, "k cache, input cleared")
+    close(vp2, vp, tight, "v cache, input cleared")
 
 
 def test_ring_keeps_only_the_last_positions_of_a_long_prompt():

@@ -498,6 +498,20 @@ static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float
     return tq_launch_status();
 }
 
+// Independent shares of K that a float32 product without gating is cut into (1: none; see dg_launch).
+static int dg_reduce_shares(int N, int K) {
+    const int tiles = (N + DG_ROWS - 1) / DG_ROWS, k_total = (K + DG_BK - 1) / DG_BK;
+    if (k_total < 16 || tq_deterministic()) return 1;
+    int splits = 2 * tq_sm_count() / tiles;
+    if (splits > k_total / 8) splits = k_total / 8;
+    return splits > 1 ? splits : 1;
+}
+
+// Whether tq_decode_gemm_tc() would cut this float32 product into independent shares of K that are added into
+// the result, which it therefore clears first unless told to accumulate.  A caller that keeps a zeroed buffer
+// can then ask for accumulation and save the clearing.
+TQ_API int tq_decode_gemm_tc_adds_shares(int N, int K) { return dg_reduce_shares(N, K) > 1 ? 1 : 0; }
+
 template <int MP, bool SWIGLU, typename TO>
 static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* Y, int M, int N, int K,
                      int ldy, int accumulate, int* status, cudaStream_t stream) {
@@ -507,11 +521,8 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
     // Float32 results without gating whose tiles do not fill the GPU's block slots (two per SM): independent
     // shares of K of at least 8 steps, as many as still run in one wave, summed by TMA.  Y must be fit for TMA
     // (16-byte aligned base and row stride).
-    const int slots = 2 * tq_sm_count();
-    if (!SWIGLU && sizeof(TO) == 4 && k_total >= 16 && !tq_deterministic() &&
-        (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (ldy & 3) == 0) {
-        int splits = slots / tiles;
-        if (splits > k_total / 8) splits = k_total / 8;
+    if (!SWIGLU && sizeof(TO) == 4 && (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (ldy & 3) == 0) {
+        const int splits = dg_reduce_shares(N, K);
         if (splits > 1)
             return dg_launch_reduce<MP>(mw, mx, bias, (float*)Y, M, N, K, ldy, accumulate, status, splits, stream);
     }

@@ -182,7 +182,7 @@ __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* _
                                       const int* __restrict__ new_lens, const int* __restrict__ block_table,
                                       int table_width, int ring_pages, int page_tokens, TC* __restrict__ q_out,
                                       TC* __restrict__ k_out, TC* __restrict__ v_out, TC* __restrict__ k_pages,
-                                      TC* __restrict__ v_pages, int nh, int nkv, int hd, int rot) {
+                                      TC* __restrict__ v_pages, int nh, int nkv, int hd, int rot, int clear_in) {
     // grid (token, head): heads 0..nh-1 are q, nh..nh+nkv-1 are k, the rest are v
     // The step's positions and tables were copied in before its first kernel ran: only qkv depends on the
     // kernel before, so the addressing is done before waiting for it.
@@ -243,6 +243,13 @@ __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* _
             if (dst) dst[d] = r;
             if (cache) cache[d] = r;
         }
+    }
+    // clear_in: this block alone has read its head's slice of qkv and leaves zeros there, so that the next
+    // product that adds its shares of K into the same buffer needs no clearing of its own
+    if (clear_in) {
+        __syncthreads();
+        TI* xz = const_cast<TI*>(x);
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) xz[d] = from_f32<TI>(0.f);
     }
 }
 
@@ -334,14 +341,14 @@ TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, c
                              const float* sin_tab, const int* tok_pos, const int* tok_seq, const int* new_lens,
                              const int* block_table, int table_width, int ring_pages, int page_tokens, void* q_out,
                              void* k_out, void* v_out, void* k_pages, void* v_pages, int cache_dtype, int n_tokens,
-                             int nh, int nkv, int hd, int rot, cudaStream_t stream) {
+                             int nh, int nkv, int hd, int rot, int clear_in, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rot <= 0 || rot > hd || (rot & 1) || page_tokens <= 0) return (int)cudaErrorInvalidValue;
     if ((k_pages == nullptr) != (v_pages == nullptr)) return (int)cudaErrorInvalidValue;
     if (k_pages && !block_table) return (int)cudaErrorInvalidValue;
     if (nh + 2 * nkv > 65535) return (int)cudaErrorInvalidValue;
     // many tokens: one block per token with 16-byte accesses; few tokens (decoding): one block per (token, head)
-    if (n_tokens >= 128 && in_dtype == TQ_F32 && cache_dtype == TQ_BF16 && rot == hd && (hd & 7) == 0 &&
+    if (!clear_in && n_tokens >= 128 && in_dtype == TQ_F32 && cache_dtype == TQ_BF16 && rot == hd && (hd & 7) == 0 &&
         (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0))
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, qkv_rope_cache_vec_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)qkv,
                              bias, cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width,
@@ -353,7 +360,7 @@ TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, c
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, qkv_rope_cache_kernel<TI, TC>, grid, dim3(threads), 0, stream, (const TI*)qkv, bias,  \
                          cos_tab, sin_tab, tok_pos, tok_seq, new_lens, block_table, table_width, ring_pages,   \
                          page_tokens, (TC*)q_out, (TC*)k_out, (TC*)v_out, (TC*)k_pages, (TC*)v_pages, nh, nkv, \
-                         hd, rot)
+                         hd, rot, clear_in)
     if (in_dtype == TQ_F32 && cache_dtype == TQ_F32) TQ_LAUNCH(float, float);
     if (in_dtype == TQ_F32 && cache_dtype == TQ_BF16) TQ_LAUNCH(float, bf16);
     if (in_dtype == TQ_BF16 && cache_dtype == TQ_BF16) TQ_LAUNCH(bf16, bf16);

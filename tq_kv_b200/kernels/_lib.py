@@ -139,7 +139,7 @@ _SIGNATURES = {
     "tq_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
     "tq_qkv_rope_cache": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                          c_int, c_int, c_int, c_int, c_void_p],
+                          c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_swiglu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "tq_add_into": [c_void_p, c_void_p, c_int, c_size_t, c_void_p],
     "tq_attention": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -158,6 +158,7 @@ _SIGNATURES = {
     "tq_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_void_p, c_void_p],
     "tq_gemm_tc_mode": [c_int],
+    "tq_decode_gemm_tc_adds_shares": [c_int, c_int],
     "tq_decode_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_void_p, c_void_p],
     "tq_flash_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,

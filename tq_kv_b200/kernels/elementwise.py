@@ -42,10 +42,11 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 def qkv_rope_cache(qkv, bias, cos, sin, tok_pos, tok_seq, new_lens, q_out, *, n_heads, n_kv_heads, head_dim,
                    rotary_dim, k_out=None, v_out=None, k_pages=None, v_pages=None, block_table=None,
-                   table_width=0, ring_pages=0, page_tokens=64):
+                   table_width=0, ring_pages=0, page_tokens=64, clear_input=False):
     """Bias, rotary encoding of q and k, head split, cache append (see
     csrc/elementwise.cu).  qkv [T, (nh+2nkv)*hd]; cos/sin float32
-    [positions, rotary_dim/2]; q_out/k_out/v_out and the pages share one dtype."""
+    [positions, rotary_dim/2]; q_out/k_out/v_out and the pages share one dtype.
+    With `clear_input` the kernel leaves zeros in the rows of qkv it has read."""
     T = qkv.shape[0]
     width = (n_heads + 2 * n_kv_heads) * head_dim
     if qkv.shape[1] != width:
@@ -64,7 +65,8 @@ def qkv_rope_cache(qkv, bias, cos, sin, tok_pos, tok_seq, new_lens, q_out, *, n_
     check(core().tq_qkv_rope_cache(
         ptr(qkv), dtype_code(qkv), ptr(bias), ptr(cos), ptr(sin), ptr(tok_pos), ptr(tok_seq), ptr(new_lens),
         ptr(block_table), table_width, ring_pages, page_tokens, ptr(q_out), ptr(k_out), ptr(v_out), ptr(k_pages),
-        ptr(v_pages), dtype_code(q_out), T, n_heads, n_kv_heads, head_dim, rotary_dim, stream()), "qkv_rope_cache")
+        ptr(v_pages), dtype_code(q_out), T, n_heads, n_kv_heads, head_dim, rotary_dim, int(clear_input), stream()),
+        "qkv_rope_cache")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor):

@@ -142,6 +142,19 @@ def _fused_norm(x: "PendingNorm", w, out, bias, accumulate, swiglu) -> bool:
     return True
 
 
+def product_adds_shares(rows: int, w: torch.Tensor) -> bool:
+    """Whether linear() of `rows` bfloat16 rows with `w` and a float32 result would run the decode product
+    that cuts K into independent shares and adds them into the result (which it clears first, unless told to
+    accumulate).  A caller that keeps a buffer of zeros can then ask for accumulation and save the clearing."""
+    N, K = w.shape
+    if not (USE_TCGEN05 and w.dtype == torch.bfloat16 and 0 < rows <= SKINNY_MAX_ROWS and K % 8 == 0
+            and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0):
+        return False
+    if not (rows > ROW_KERNEL_MAX_ROWS or w.numel() * 2 >= TC_DECODE_MIN_WEIGHT_BYTES or K % 32):
+        return False                                   # the mma.sync kernel takes it
+    return bool(core().tq_decode_gemm_tc_adds_shares(N, K))
+
+
 def _tc_ok(x, w, out, swiglu) -> bool:
     return (USE_TCGEN05 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0

@@ -23,6 +23,7 @@ from .registry import make_part
 
 class GQAttention(Mixer):
     takes_pending_norm = True           # x goes to kernels.linear only
+    ZERO_BUFFER_ROWS = 64               # decode steps of up to this many rows use the shared q/k/v buffer
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -72,6 +73,12 @@ class GQAttention(Mixer):
         if self.out_bias:
             self.b_o = float32_vector(tensors[self._n("o", "bias")])
         self.window_chunk = runtime.window_chunk
+        key = ("qkv kept zero", self.q_width + 2 * self.kv_width, str(runtime.device))
+        store = shared if shared is not None else {}
+        if key not in store:                               # one buffer for all layers of this width, and its flag
+            store[key] = (torch.zeros((self.ZERO_BUFFER_ROWS, self.q_width + 2 * self.kv_width),
+                                      dtype=torch.float32, device=runtime.device), [False])
+        self._qkv_zero = store[key]
         self.position.bind(tensors, runtime, shared)      # a position encoding may have tensors of its own
         self.position.prepare(runtime, shared)
 
@@ -102,13 +109,29 @@ class GQAttention(Mixer):
         act = ctx.runtime.act_dtype
         owns = kv is not None and kv.writes
         packed = self._use_packed(b.host_start, b.host_lens, owns)
-        qkv = kernels.linear(x, self.w_qkv, out_dtype=torch.float32)
+        # Where a decode step's q/k/v product adds shares of K into its result, the result must start at zero.
+        # Instead of clearing it before every product, the layers share one buffer that is zero between uses:
+        # the rotary kernel, which alone reads it, leaves zeros behind.
+        kept_zero = (T <= self.ZERO_BUFFER_ROWS and act == torch.bfloat16
+                     and getattr(self.position, "clears_input", False)
+                     and kernels.product_adds_shares(T, self.w_qkv))
+        if kept_zero:
+            buf, dirty = self._qkv_zero
+            if dirty[0]:                                   # a step failed between the product and the rotary kernel
+                buf.zero_()
+            dirty[0] = True
+            qkv = kernels.linear(x, self.w_qkv, out=buf[:T], accumulate=True)
+        else:
+            qkv = kernels.linear(x, self.w_qkv, out_dtype=torch.float32)
         kernels.mark("qkv")
         q = torch.empty((T, self.q_width), dtype=act, device=dev)
         k = torch.empty((T, self.kv_width), dtype=act, device=dev) if packed else None
         v = torch.empty((T, self.kv_width), dtype=act, device=dev) if packed else None
+        extra = {"clear_input": True} if kept_zero else {}
         self.position.encode_and_store(qkv, self.b_qkv, ctx, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
-                                       head_dim=self.head_dim, q_out=q, k_out=k, v_out=v)
+                                       head_dim=self.head_dim, q_out=q, k_out=k, v_out=v, **extra)
+        if kept_zero:
+            self._qkv_zero[1][0] = False
         kernels.mark("rotary")
         out = torch.empty_like(q)
         common = dict(n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,

@@ -46,7 +46,10 @@ class RotaryHalved(PositionEncoding):
         if shared is not None:
             shared[key] = (self.cos, self.sin)
 
-    def encode_and_store(self, qkv, bias, ctx: StepContext, *, n_heads, n_kv_heads, head_dim, q_out, k_out, v_out):
+    clears_input = True          # encode_and_store(..., clear_input=True) leaves zeros in qkv
+
+    def encode_and_store(self, qkv, bias, ctx: StepContext, *, n_heads, n_kv_heads, head_dim, q_out, k_out, v_out,
+                         clear_input=False):
         b = ctx.batch
         kv = ctx.kv
         write = kv is not None and kv.writes
@@ -57,4 +60,4 @@ class RotaryHalved(PositionEncoding):
             k_out=k_out, v_out=v_out,
             k_pages=kv.k_pages if write else None, v_pages=kv.v_pages if write else None,
             block_table=table, table_width=width, ring_pages=kv.ring_pages if write else 0,
-            page_tokens=kv.page_tokens if kv is not None else 64)
+            page_tokens=kv.page_tokens if kv is not None else 64, clear_input=clear_input)
