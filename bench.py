@@ -230,7 +230,7 @@ def main() -> int:
     if unequal:
         lengths = torch.randint(64, 4097, (args.batch,), generator=gen).tolist()
         max_b = args.batch
-        room = max(K + W, args.e2e_steps + max(W, 16) + 1) + 2
+        room = max(K + W, max(args.e2e_steps, K) + max(W, 16) + 1) + 2
         max_tokens = sum(-(-(n + room) // 64) * 64 for n in lengths)
     else:
         lengths = None
@@ -297,20 +297,22 @@ def main() -> int:
         prompt's matrix products left behind); then `steps` steps are timed between the arrivals of their
         tokens on the host."""
         stamps: list[float] = []
-        last = len(prompts) - 1
+        B = len(prompts)
 
         def on_token(i, t):
-            if i == last:
-                stamps.append(time.perf_counter())         # the token is on the host now
+            stamps.append(time.perf_counter())             # the token is on the host now
 
         h2d0, stats = engine.h2d_bytes, {}
         engine.generate(prompts, tq.GenerationParams.greedy(e2e_warmup + steps + 1, stop_token_ids=()),
                         on_token=on_token, stats=stats)
-        timed = stamps[e2e_warmup:]
-        n = len(stamps)
-        value = len(prompts) * (len(timed) - 1) / (timed[-1] - timed[0])
-        h2d = (engine.h2d_bytes - h2d0 + stats.get("h2d_bytes", 0)) / n
-        return value, int(h2d), int(stats.get("d2h_bytes", 0) / n), len(timed) - 1
+        # every request yields the same number of tokens, a round of the batch at a time: the clock starts with
+        # the last token of the last warm-up round
+        first = e2e_warmup * B - 1
+        n_timed = len(stamps) - 1 - first
+        value = n_timed / (stamps[-1] - stamps[first])
+        rounds = len(stamps) / B
+        h2d = (engine.h2d_bytes - h2d0 + stats.get("h2d_bytes", 0)) / rounds
+        return value, int(h2d), int(stats.get("d2h_bytes", 0) / rounds), n_timed // B
 
     def e2e_prompt(steps: int) -> int:
         """Prompt length at which `steps` generated tokens see the same mean context as the device-timed steps."""

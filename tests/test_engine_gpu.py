@@ -361,3 +361,27 @@ def test_a_wait_that_ran_out_in_a_replayed_step_surfaces_in_short_runs(tmp_root)
         kernels.check_tc_status()
         if s is not None:
             eng.release(s)
+
+
+def test_a_step_that_fails_after_reserving_gives_its_pages_back(tmp_root, monkeypatch):
+    """An error inside the step (here: the model's forward raises) leaves lengths as they were and returns the
+    pages that the step had reserved; the next step runs as if nothing had happened."""
+    from tq_kv_b200.engine import StepRow
+    eng, folder = engine_for(tmp_root, "a", "float32", max_tokens=384)
+    toks = random_tokens(150, TINY["a"]["vocab_size"], 91)
+    s = eng.new_sequence()
+    eng.step([StepRow(s, toks[:10], [])])
+    free = eng.cache.free_pages()
+
+    def boom(*a, **k):
+        raise RuntimeError("boom")
+
+    monkeypatch.setattr(eng.model, "forward", boom)
+    with pytest.raises(RuntimeError, match="boom"):
+        eng.step([StepRow(s, toks[10:150], [])])             # would have taken two more pages
+    monkeypatch.undo()
+    assert eng.length(s) == 10 and eng.cache.free_pages() == free
+    eng.cache.book.check()
+    got = eng.step([StepRow(s, toks[10:150], [139])])
+    assert_close(got, plain_logits(folder, toks)[149:150], "float32", "after a failed step")
+    eng.release(s)

@@ -79,7 +79,8 @@ def bench_decode_gemm(args) -> None:
         ws = _copies(2 * N if swiglu else N, K, 0.02)
         x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
         out = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16 if swiglu else torch.float32)
-        us = _time(lambda i: gemm.linear(x, ws[i], out=out, accumulate=acc, swiglu=swiglu), len(ws), args.reps)
+        us = _time(lambda i: gemm.linear(x, ws[i], out=out, accumulate=acc, swiglu=swiglu), len(ws), args.reps,
+                   graph=True)         # small products are otherwise timed at the pace of Python's launches
         print(f"{name:8s} {M} x {N} x {K}  {us:8.1f} us  {ws[0].numel() * 2 / us / 1e6:5.2f} TB/s of weights")
     check_tc_status()
 
