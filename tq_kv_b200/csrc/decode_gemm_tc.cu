@@ -310,6 +310,11 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
+                    if (k_splits == 1 && !accumulate)      // the only share of a result that is not added to: a store
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];\n"
+                            ::"l"(&map_y), "r"(n0 + quarter * 32), "r"(0), "r"(dg_smem(piece)) : "memory");
+                    else
                     asm volatile(
                         "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];\n"
                         ::"l"(&map_y), "r"(n0 + quarter * 32), "r"(0), "r"(dg_smem(piece)) : "memory");
@@ -451,13 +456,13 @@ static int dg_launch_reduce(const CUtensorMap& mw, const CUtensorMap& mx, const 
                                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return 1000 + (int)r;
     }
-    if (!accumulate) {
+    if (!accumulate && splits > 1) {                      // several shares are added into a cleared result
         cudaError_t e = cudaMemset2DAsync(Y, (size_t)ldy * 4, 0, (size_t)N * 4, (size_t)M, stream);
         if (e != cudaSuccess) return (int)e;
     }
     const int tiles = (N + DG_ROWS - 1) / DG_ROWS;
     return tq_launch_pdl(TQ_PDL_DECODE_GEMM, decode_gemm_tc_kernel<MP, false, float, STAGES, true>, dim3(tiles * splits), dim3(DG_THREADS),
-                         SMEM, stream, mw, mx, my, bias, Y, M, N, K, ldy, 1, splits, status, (const float*)nullptr, 0,
+                         SMEM, stream, mw, mx, my, bias, Y, M, N, K, ldy, accumulate, splits, status, (const float*)nullptr, 0,
                          (const float*)nullptr, 0.f);
 }
 
@@ -522,14 +527,13 @@ static int dg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* 
     constexpr int OUT_COLS = SWIGLU ? DG_ROWS / 2 : DG_ROWS;
     const int tiles = (N + OUT_COLS - 1) / OUT_COLS;
     const int k_total = (K + DG_BK - 1) / DG_BK;
-    // Float32 results without gating whose tiles do not fill the GPU's block slots (two per SM): independent
-    // shares of K of at least 8 steps, as many as still run in one wave, summed by TMA.  Y must be fit for TMA
-    // (16-byte aligned base and row stride).
-    if (!SWIGLU && sizeof(TO) == 4 && (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (ldy & 3) == 0) {
-        const int splits = dg_reduce_shares(N, K);
-        if (splits > 1)
-            return dg_launch_reduce<MP>(mw, mx, bias, (float*)Y, M, N, K, ldy, accumulate, status, splits, stream);
-    }
+    // Float32 results without gating: where the tiles do not fill the GPU's block slots (two per SM), independent
+    // shares of K, as many as still run in one wave (dg_reduce_shares).  These results leave through TMA (a store for a single share that is not added to anything,
+    // else a reduce-add), which costs a block far less than the exchange and the element-wise stores of the
+    // cluster form below.  Y must be fit for TMA (16-byte aligned base and row stride).
+    if (!SWIGLU && sizeof(TO) == 4 && (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (ldy & 3) == 0)
+        return dg_launch_reduce<MP>(mw, mx, bias, (float*)Y, M, N, K, ldy, accumulate, status, dg_reduce_shares(N, K),
+                                    stream);
     // split K while the grid is small and the shares stay long.  Measured best on the 7B shapes: up to 4
     // blocks and about 64 blocks in all for batches over 16 rows, up to 8 and a full GPU for smaller ones.
     const int max_ranks = M > 16 ? 4 : 8, want_blocks = M > 16 ? 64 : tq_sm_count();
