@@ -400,8 +400,8 @@ def main() -> int:
         if not unequal:
             points = {}
             for b in (1, 64):
-                steps_b = max(16, min(K, 64))
-                ms_b, _ = decode_run([start_ctx] * b, steps_b, max(3, min(W, 4)))
+                steps_b = max(64, min(K, 128))
+                ms_b, _ = decode_run([start_ctx] * b, steps_b, max(W, 16))      # (the clocks settle, as for e2e)
                 points[f"decode_b{b}"] = round(b * steps_b / (ms_b / 1e3), 1)
                 if not args.no_e2e:
                     n_e2e = min(args.e2e_steps, args.context - args.prompt - e2e_warmup - 2)
