@@ -95,7 +95,8 @@ def generate(engine, prompts: Sequence[Sequence[int]], params: Optional[Generati
         free_slots=cache.free_slots, free_pages=cache.free_pages(), max_context=engine.runtime.max_context)
     for batch in batches:
         sampler = sampler_factory(params, len(batch), engine.vocab_size, engine.runtime.device)
-        ahead = getattr(engine, "sampled", None) is not None and hasattr(sampler, "sample_device")
+        ahead = (getattr(engine, "sampled", None) is not None and hasattr(sampler, "sample_device")
+                 and len(batch) <= engine.sampled.rows)
         if pipeline is False or not ahead:
             _run_batch(engine, prompts, batch, params, stop, results, on_token, sampler, stats)
         else:
