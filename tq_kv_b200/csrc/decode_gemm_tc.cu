@@ -403,7 +403,8 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     if (SWIGLU) w /= rms;
                 }
                 if (bias) { v += bias[col]; if (SWIGLU) w += bias[col + N]; }
-                if (SWIGLU) v = (v / (1.f + expf(-v))) * w;
+                if (SWIGLU)            // (a bfloat16 result keeps 8 bits: the fast exponential and division do)
+                    v = sizeof(TO) == 2 ? __fdividef(v, 1.f + __expf(-v)) * w : (v / (1.f + expf(-v))) * w;
                 TO* y = Y + (size_t)m * ldy + col;
                 if (accumulate) v += to_f32<TO>(*y);
                 *y = from_f32<TO>(v);

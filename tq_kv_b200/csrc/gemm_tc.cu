@@ -152,8 +152,12 @@ __device__ __forceinline__ void tc_epilogue_item(uint32_t t_row, unsigned char* 
             tc_ld32(t_row + c, v);
             tc_ld32(t_row + TC_BN / 2 + c, u);
             tc_wait_ld();
+            // silu(g) * u.  A bfloat16 result keeps 8 bits: the fast exponential and division (2 ulp of float32)
+            // cost a third of the exact ones' instructions, which a short K cannot hide under its MMAs.
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = (v[j] / (1.f + expf(-v[j]))) * u[j];
+            for (int j = 0; j < 32; ++j)
+                v[j] = sizeof(TO) == 2 ? __fdividef(v[j], 1.f + __expf(-v[j])) * u[j]
+                                       : (v[j] / (1.f + expf(-v[j]))) * u[j];
         } else {
             tc_ld32(t_row + c, v);
             tc_wait_ld();

@@ -227,7 +227,8 @@ skinny_gemm_kernel(const void* __restrict__ Xv, const bf16* __restrict__ W, cons
                 if (SWIGLU) u /= rms;
             }
             if (bias) { v += bias[col]; if (SWIGLU) u += bias[col + N]; }
-            if (SWIGLU) v = (v / (1.f + expf(-v))) * u;
+            if (SWIGLU)                // (a bfloat16 result keeps 8 bits: the fast exponential and division do)
+                v = sizeof(TO) == 2 ? __fdividef(v, 1.f + __expf(-v)) * u : (v / (1.f + expf(-v))) * u;
             TO* y = Y + (size_t)m * ldy + col;
             if (accumulate) v += to_f32<TO>(*y);
             *y = from_f32<TO>(v);
