@@ -507,11 +507,12 @@ static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float
 // Independent shares of K that a float32 product without gating is cut into (1: none; see dg_launch).
 static int dg_reduce_shares(int N, int K) {
     const int tiles = (N + DG_ROWS - 1) / DG_ROWS, k_total = (K + DG_BK - 1) / DG_BK;
-    // Shares of at least 8 steps where K is long; of 2 where it is short (a narrow model's projections: 14 steps
-    // in all), since the cluster form's exchange through shared memory costs such a small product more than its
-    // whole main loop (measured at 64 rows, 896 x 896: 26 us in the cluster form, 4 us in this one).
+    // As many shares as fill the block slots once, down to two steps of 64 each (one where K is short).  Measured
+    // alone in a replayed graph: shares of 8 steps against 2 cost the 7B shape's o product 7.9 against 7.1 us, a
+    // 2048 x 2048 one 5.5 against 4.3, 896 x 4864 5.8 against 4.5.  (The cluster form's exchange through shared
+    // memory costs a small product more than its whole main loop: 64 rows, 896 x 896, 26 us there and 4 us here.)
     if (k_total < 4 || tq_deterministic()) return 1;
-    const int per_share = k_total >= 32 ? 8 : 2;
+    const int per_share = k_total >= 24 ? 2 : 1;
     int splits = 2 * tq_sm_count() / tiles;
     if (splits > k_total / per_share) splits = k_total / per_share;
     return splits > 1 ? splits : 1;

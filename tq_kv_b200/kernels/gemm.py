@@ -1,10 +1,10 @@
 """Matrix products: y = x · W^T with W stored [out, in].
 
 `linear()` picks the kernel from the operands:
-  * up to 16 rows of bfloat16 and weights under 24 MB (decoding a small
-    model): the weight-streaming mma.sync kernel of csrc/skinny_gemm.cu, which
-    reads the weight once and fuses bias, SwiGLU gating and the float32
-    accumulation into the residual stream;
+  * up to 16 rows of bfloat16 and small weights (decoding a small model; the
+    limits are in `_tc_takes`): the weight-streaming mma.sync kernel of
+    csrc/skinny_gemm.cu, which reads the weight once and fuses bias, SwiGLU
+    gating and the float32 accumulation into the residual stream;
   * up to 64 rows of bfloat16 otherwise: the same job on tcgen05 with swapped
     operands, TMA-fed (csrc/decode_gemm_tc.cu);
   * up to 16 rows of anything else: the float32 row kernel of csrc/gemm.cu
@@ -67,7 +67,31 @@ FUSE_NORM = {"1": True, "0": False}.get(os.environ.get("TQ_FUSE_NORM", ""), "aut
 FUSED_NORM_MAX_ROWS = 16
 ROW_KERNEL_MAX_ROWS = 16
 SKINNY_MAX_ROWS = 64
-TC_DECODE_MIN_WEIGHT_BYTES = 24 << 20      # see linear()
+# Weights from which a decode product of up to 16 rows runs on the tcgen05 kernel (see _tc_takes)
+TC_DECODE_MIN_WEIGHT_BYTES = 24 << 20      # the product after a pending norm
+TC_DECODE_MIN_GATED_BYTES = 64 << 20       # gated products
+TC_DECODE_MIN_ADDED_BYTES = 4 << 20        # float32 results of given rows, which leave as shares of K
+TC_DECODE_ADDED_ROWS = 8                   # ... and these from 9 rows on at any size
+
+
+def _tc_takes(rows: int, w: torch.Tensor, swiglu: bool, after_norm: bool, float32_out: bool) -> bool:
+    """Which of the two decode kernels gets a bfloat16 product that both can run: True for the TMA-fed
+    tcgen05 kernel, False for the mma.sync one.  Over 16 rows always the former.  Below that by the weight's
+    size, with limits that were measured (each product alone in a replayed graph, and the whole decode step
+    of the 7B and 0.5B shapes): the product after a pending norm from 24 MB on (below it the mma.sync kernel
+    with the norm folded in wins: 6 MB q|k|v 4.4 against 3.8 + a norm kernel); gated products from 64 MB on
+    (55 MB at 8 rows: 12.8 against 14.3 us; 90 MB: 21.0 against 20.1); float32 results of rows that are
+    given, which the tcgen05 kernel cuts into shares of K that meet in the L2, from 4 MB on and from 9 rows on
+    at any size (9 MB with K = 4,864 at 8 rows: 6.1 against 4.5 us, at 16 rows 8.6 against 4.8; 5 MB with
+    K = 1,536: 4.5 against 3.2; 1.6 MB at 8 rows: 2.9 against 2.7, a tie left where it was)."""
+    if rows > ROW_KERNEL_MAX_ROWS or w.shape[1] % 32:
+        return True
+    size = w.numel() * 2
+    if swiglu:
+        return size >= TC_DECODE_MIN_GATED_BYTES
+    if after_norm or not float32_out:
+        return size >= TC_DECODE_MIN_WEIGHT_BYTES
+    return size >= TC_DECODE_MIN_ADDED_BYTES or rows > TC_DECODE_ADDED_ROWS
 
 
 def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
@@ -120,7 +144,7 @@ def _fused_norm(x: "PendingNorm", w, out, bias, accumulate, swiglu) -> bool:
     """Runs out (=, +=) norm(h) . w^T with the norm folded into a decode product; False if none takes it."""
     h, g = x.h, x.weight
     M, K = h.shape
-    big = w.numel() * 2 >= TC_DECODE_MIN_WEIGHT_BYTES or K % 32 != 0          # the tcgen05 kernel's case
+    big = _tc_takes(M, w, bool(swiglu), True, out.dtype == torch.float32)     # the tcgen05 kernel's case
     # Measured inside whole decode steps: the tcgen05 kernel gains from the folded norm where it runs in its
     # cluster form anyway (gated products: 7B shape -0.8 % of a step) and loses where the norm costs it the
     # form with independent shares of K (float32 results: +8 %); the mma.sync kernel gains for plain products
@@ -144,15 +168,16 @@ def _fused_norm(x: "PendingNorm", w, out, bias, accumulate, swiglu) -> bool:
     return True
 
 
-def product_adds_shares(rows: int, w: torch.Tensor) -> bool:
-    """Whether linear() of `rows` bfloat16 rows with `w` and a float32 result would run the decode product
-    that cuts K into independent shares and adds them into the result (which it clears first, unless told to
-    accumulate).  A caller that keeps a buffer of zeros can then ask for accumulation and save the clearing."""
+def product_adds_shares(rows: int, w: torch.Tensor, after_norm: bool = True) -> bool:
+    """Whether linear() of `rows` bfloat16 rows (the result of a pending norm, or given rows) with `w` and a
+    float32 result would run the decode product that cuts K into independent shares and adds them into the
+    result (which it clears first, unless told to accumulate).  A caller that keeps a buffer of zeros can then
+    ask for accumulation and save the clearing."""
     N, K = w.shape
     if not (USE_TCGEN05 and w.dtype == torch.bfloat16 and 0 < rows <= SKINNY_MAX_ROWS and K % 8 == 0
             and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0):
         return False
-    if not (rows > ROW_KERNEL_MAX_ROWS or w.numel() * 2 >= TC_DECODE_MIN_WEIGHT_BYTES or K % 32):
+    if not _tc_takes(rows, w, False, after_norm, True):
         return False                                   # the mma.sync kernel takes it
     return bool(core().tq_decode_gemm_tc_adds_shares(N, K))
 
@@ -223,13 +248,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
             return out
         x = pending.materialize()
 
-    # decoding: the TMA-fed tcgen05 kernel for batches over 16 rows and for weights from 24 MB on at any batch,
-    # the mma.sync kernel for smaller weights at small batches.  The limit was set inside the whole decode step
-    # (the 7B shape's 26 and 33 MB products are 4 % of a step faster on the TMA kernel, the 0.5B shape's 9 and
-    # 17 MB products 5 % slower); timed alone, back to back, the mma.sync kernel looks faster up to 64 MB.
+    # decoding: the TMA-fed tcgen05 kernel or the mma.sync kernel (_tc_takes says which, where both can)
     if (USE_TCGEN05 and M <= SKINNY_MAX_ROWS and _tc_ok(x, w, out, swiglu)
             and (not accumulate or out.dtype == torch.float32)
-            and (M > ROW_KERNEL_MAX_ROWS or w.numel() * 2 >= TC_DECODE_MIN_WEIGHT_BYTES or not _skinny_ok(x, w))):
+            and (not _skinny_ok(x, w)
+                 or _tc_takes(M, w, bool(swiglu), pending is not None, out.dtype == torch.float32))):
         return decode_gemm_tc(x, w, out, bias, accumulate, swiglu)
     if _skinny_ok(x, w):
         return skinny_gemm(x, w, out, bias, accumulate, swiglu)

@@ -114,7 +114,7 @@ class GQAttention(Mixer):
         # the rotary kernel, which alone reads it, leaves zeros behind.
         kept_zero = (T <= self.ZERO_BUFFER_ROWS and act == torch.bfloat16
                      and getattr(self.position, "clears_input", False)
-                     and kernels.product_adds_shares(T, self.w_qkv))
+                     and kernels.product_adds_shares(T, self.w_qkv, isinstance(x, kernels.PendingNorm)))
         if kept_zero:
             buf, dirty = self._qkv_zero
             if dirty[0]:                                   # a step failed between the product and the rotary kernel
