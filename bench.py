@@ -366,7 +366,7 @@ def main() -> int:
                    "seq_len": args.context,
                    "prompt_len": "uniform 64..4096, seed 0" if unequal else args.prompt,
                    "decode_ctx_start": round(sum(ctx_lens) / args.batch) + W,
-                   "cache_tokens": engine.cache.groups[0].book.pool.n * 64,
+                   "cache_tokens": engine.cache.groups[0].book.n_pages * 64,
                    "parallelism": "single GPU", "weights": "random N(0,0.02) bf16",
                    "l2": f"a step reads {step_bytes / 1e9:.1f} GB of weights and cache, more than the 126 MB L2",
                    "peaks": pk_src},

@@ -1,40 +1,44 @@
-"""The cache's bookkeeping: no slot or page lost, held twice or freed twice
-(CPU; storage on the CPU device is only memory, no kernel runs)."""
+"""The cache's bookkeeping (the host runtime, csrc/host_runtime.cpp, through its Python face): no slot or
+page lost, held twice or freed twice; the checks of a step; the packing of a step's rows (CPU; storage on the CPU
+device is only memory, no kernel runs)."""
 import random
 
+import numpy as np
 import pytest
 import torch
 
-from tq_kv_b200.cache import (CacheError, GroupPages, IndexPool, KVRequest, SequenceCache, SlotBook, StateRequest,
+from tq_kv_b200.cache import (CacheError, KVRequest, PageGroup, SequenceCache, SlotBook, StateRequest, StepError,
                               PAGE_TOKENS)
 
 
-def test_index_pool_lowest_first_and_reuse():
-    p = IndexPool(3, "slot")
-    assert [p.take(), p.take(), p.take()] == [0, 1, 2]
+def test_slots_lowest_first_and_reuse():
+    b = SlotBook(3, [], 100)
+    assert [b.alloc(), b.alloc(), b.alloc()] == [0, 1, 2]
     with pytest.raises(CacheError, match="no free slot"):
-        p.take()
-    p.give_back(1)
-    p.give_back(0)
-    assert p.take() == 0 and p.take() == 1
-    p.check()
+        b.alloc()
+    b.free(1)
+    b.free(0)
+    assert b.alloc() == 0 and b.alloc() == 1
+    b.check()
 
 
 def test_double_free_and_foreign_handles_raise():
-    p = IndexPool(2, "slot")
-    s = p.take()
-    p.give_back(s)
+    b = SlotBook(2, [], 100)
+    s = b.alloc()
+    b.free(s)
     with pytest.raises(CacheError, match="freed twice"):
-        p.give_back(s)
+        b.free(s)
     with pytest.raises(CacheError, match="does not exist"):
-        p.give_back(5)
-    p.check()
+        b.free(5)
+    with pytest.raises(CacheError, match="not held"):
+        b.length(s)
+    b.check()
 
 
 def _book(slots=4, pages=8, ring=None, max_len=10_000):
-    groups = [GroupPages("full", pages, PAGE_TOKENS, None)]
+    groups = [PageGroup("full", pages, PAGE_TOKENS, None)]
     if ring:
-        groups.append(GroupPages("win", pages, PAGE_TOKENS, ring))
+        groups.append(PageGroup("win", pages, PAGE_TOKENS, ring))
     return SlotBook(slots, groups, max_len)
 
 
@@ -42,12 +46,13 @@ def test_pages_follow_lengths_and_come_back():
     b = _book(ring=2)
     s = b.alloc()
     b.reserve([s], [65]); b.commit([s], [65])
-    assert len(b.groups[0].pages[s]) == 2 and len(b.groups[1].pages[s]) == 2
+    assert len(b.pages(0, s)) == 2 and len(b.pages(1, s)) == 2
     b.reserve([s], [64]); b.commit([s], [64])
-    assert len(b.groups[0].pages[s]) == 3 and len(b.groups[1].pages[s]) == 2     # the ring stops growing
+    assert len(b.pages(0, s)) == 3 and len(b.pages(1, s)) == 2     # the ring stops growing
+    assert b.pages(0, s) == [0, 1, 2]                              # pages are handed out lowest first
     b.check()
     b.free(s)
-    assert b.groups[0].pool.free_count == 8 and b.groups[1].pool.free_count == 8 and s not in b.length
+    assert b.free_pages(0) == 8 and b.free_pages(1) == 8 and not b.is_held(s)
     with pytest.raises(CacheError, match="freed twice"):
         b.free(s)
     b.check()
@@ -57,10 +62,10 @@ def test_reserve_is_all_or_nothing():
     b = _book(pages=3)
     s0, s1 = b.alloc(), b.alloc()
     b.reserve([s0], [100]); b.commit([s0], [100])                  # 2 pages
-    before = (b.groups[0].pool.free_count, dict(b.length))
+    before = (b.free_pages(0), b.lengths([s0, s1]))
     with pytest.raises(CacheError, match="is full"):
         b.reserve([s0, s1], [28, 65])                               # s0 fits in its pages, s1 needs 2, 1 is free
-    assert (b.groups[0].pool.free_count, dict(b.length)) == before and s1 not in b.groups[0].pages
+    assert (b.free_pages(0), b.lengths([s0, s1])) == before and b.pages(0, s1) == []
     with pytest.raises(CacheError, match="named twice"):
         b.reserve([s0, s0], [1, 1])
     with pytest.raises(CacheError, match="not held"):
@@ -81,11 +86,14 @@ def test_context_limit():
 def test_random_walk_keeps_every_invariant():
     rng = random.Random(0)
     b = _book(slots=5, pages=12, ring=2)
-    live = []
+    live, length = [], {}
     for _ in range(2000):
         op = rng.random()
         if op < 0.3 and len(live) < 5:
-            live.append(b.alloc())
+            s = b.alloc()
+            assert s not in live                                # no slot is held twice
+            live.append(s)
+            length[s] = 0
         elif op < 0.5 and live:
             b.free(live.pop(rng.randrange(len(live))))
         elif live:
@@ -94,16 +102,23 @@ def test_random_walk_keeps_every_invariant():
             try:
                 b.reserve(rows, n)
                 b.commit(rows, n)
+                for s, k in zip(rows, n):
+                    length[s] += k
             except CacheError:
                 pass
         b.check()
-        for g in b.groups:
+        held = [set(), set()]
+        for gi, g in enumerate(b.groups):
             for s in live:
-                assert len(g.pages.get(s, [])) >= g.pages_for_length(b.length[s])
+                pages = b.pages(gi, s)
+                assert len(pages) >= g.pages_for_length(length[s]) and b.length(s) == length[s]
+                assert not held[gi] & set(pages)                # no page is held by two slots
+                held[gi] |= set(pages)
+            assert len(held[gi]) == g.n_pages - b.free_pages(gi)    # and none is lost
     for s in live:
         b.free(s)
     b.check()
-    assert all(g.pool.free_count == g.pool.n for g in b.groups) and b.slots.free_count == 5
+    assert all(b.free_pages(gi) == g.n_pages for gi, g in enumerate(b.groups)) and b.free_slots == 5
 
 
 def test_sequence_cache_groups_and_state():
@@ -133,19 +148,75 @@ def test_trim_gives_back_pages_reserved_for_a_step_that_did_not_happen():
     s = b.alloc()
     b.reserve([s], [70])
     b.commit([s], [70])
-    before = {g.name: list(g.pages[s]) for g in b.groups}
+    before = [b.pages(gi, s) for gi in range(2)]
     b.reserve([s], [200])                       # the step then fails: nothing is committed
-    held = b.groups[0].pages[s]
-    assert len(held) == 5
+    assert len(b.pages(0, s)) == 5
     b.trim([s])
-    assert {g.name: g.pages[s] for g in b.groups} == before
-    assert b.groups[0].pages[s] is not held     # a new list, so that cached views of the old one are seen stale
-    assert b.groups[0].pool.free_count == 6
+    assert [b.pages(gi, s) for gi in range(2)] == before
+    assert b.free_pages(0) == 6
     b.check()
     b.trim([s])                                 # nothing to give back: no change
     b.check()
     b.free(s)
-    assert b.groups[0].pool.free_count == 8 and b.groups[1].pool.free_count == 8
+    assert b.free_pages(0) == 8 and b.free_pages(1) == 8
+
+
+def test_the_checks_of_a_step_refuse_before_anything_changes():
+    b = _book(slots=3, pages=4)
+    s0, s1 = b.alloc(), b.alloc()
+    ok = dict(slots=[s0, s1], lens=[3, 1], tokens=[5, 6, 7, 8], want_counts=[2, 1], want=[0, 2, 0], sources=[-1, -1],
+              vocab=10, source_rows=4)
+    b.begin_step(**ok)
+    for change, message in [
+            (dict(lens=[0, 1], tokens=[8], want_counts=[0, 1], want=[0]), "Empty prompt"),
+            (dict(tokens=[5, 6, 10, 8]), "token id 10 is outside the vocabulary"),
+            (dict(tokens=[5, -1, 7, 8]), "outside the vocabulary"),
+            (dict(want=[0, 3, 0]), "wanted place 3 is outside the 3 tokens"),
+            (dict(slots=[s0, 2]), "slot 2 is not held"),
+            (dict(sources=[1, -1]), "exactly one token"),
+            (dict(sources=[-1, 4]), "exactly one token")]:
+        with pytest.raises(StepError, match=message):
+            b.begin_step(**{**ok, **change})
+    b.begin_step(**{**ok, "sources": [-1, 3], "tokens": [5, 6, 7, 99]})    # a row fed on the device: its id is not looked at
+    with pytest.raises(StepError, match="at least one row"):
+        b.begin_step([], [], [], [], [], [], 10, 4)
+    assert b.free_pages(0) == 4 and b.lengths([s0, s1]) == [0, 0]
+    b.check()
+
+
+def test_a_packed_step_holds_what_the_kernels_read():
+    b = _book(slots=3, pages=6, ring=2)
+    s0, s1 = b.alloc(), b.alloc()
+    b.reserve([s0], [70]); b.commit([s0], [70])                    # s0 holds 70 tokens already
+    slots, lens, tokens = [s1, s0], [3, 2], [11, 12, 13, 21, 22]
+    want_counts, want, sources = [1, 2], [2, 0, 1], [-1, -1]
+    b.reserve(slots, lens)
+    lay = b.step_layout(slots, lens, want_counts)
+    assert all(o % 4 == 0 for o in lay.offs) and lay.widths.tolist() == [2, 2]
+    buf = np.full(lay.total, -7, dtype=np.int32)
+    b.pack_step(slots, lens, tokens, want_counts, want, sources, lay, buf)
+    o = lay.offs
+    seg = lambda i, n: buf[o[i]:o[i] + n].tolist()
+    assert seg(0, 5) == tokens and seg(1, 5) == [0, 0, 0, 1, 1] and seg(2, 5) == [0, 1, 2, 70, 71]
+    assert seg(3, 3) == [0, 3, 5] and seg(4, 2) == [s1, s0] and seg(5, 2) == [0, 70] and seg(6, 2) == [3, 72]
+    assert seg(7, 3) == [2, 3, 4] and seg(8, 5) == [-1] * 5
+    assert seg(9, 4) == b.pages(0, s1) + [0] + b.pages(0, s0) and seg(10, 4) == b.pages(1, s1) + [0] + b.pages(1, s0)
+    b.commit(slots, lens)
+    # a decode step of the same two rows into a buffer of fixed layout: full-width tables
+    offs = np.asarray([0, 4, 8, 12, 16, 20, 24, 28, 32, 36, 48], dtype=np.int32)
+    widths = np.asarray([5, 2], dtype=np.int32)
+    dec = np.full(60, -7, dtype=np.int32)
+    b.reserve(slots, [1, 1])
+    b.pack_decode(np.asarray(slots, dtype=np.int32), np.asarray([31, 0], dtype=np.int32),
+                  np.asarray([-1, 3], dtype=np.int32), offs, widths, dec.ctypes.data)
+    assert dec[0:2].tolist() == [31, 0] and dec[32:34].tolist() == [-1, 3] and dec[8:10].tolist() == [3, 72]
+    assert dec[16:18].tolist() == [s1, s0] and dec[20:22].tolist() == [3, 72] and dec[24:26].tolist() == [4, 73]
+    assert dec[36:37].tolist() == b.pages(0, s1) and dec[41:43].tolist() == b.pages(0, s0)
+    assert dec[48:49].tolist() == b.pages(1, s1) and dec[50:52].tolist() == b.pages(1, s0)
+    with pytest.raises(StepError, match="table has room for 1"):
+        b.pack_decode(np.asarray(slots, dtype=np.int32), np.asarray([31, 0], dtype=np.int32),
+                      np.asarray([-1, 3], dtype=np.int32), offs, np.asarray([1, 2], dtype=np.int32), dec.ctypes.data)
+    b.check()
 
 
 def test_ring_holds_the_window_plus_the_slack():

@@ -1,7 +1,10 @@
-"""Bookkeeping of the cache, all on the host and free of torch: which slots
-are held, which pages each slot holds in each group, how long each sequence
-is.  Every misuse (no slot left, a slot freed twice, a page held twice) raises
-before anything is launched.
+"""Bookkeeping of the cache and the host side of a step: which slots are held,
+which pages each slot holds in each group, how long each sequence is; the
+checks a step must pass before anything is launched; the packing of a step's
+rows into one int32 buffer.  All of it lives in the host runtime
+(csrc/host_runtime.cpp: C++, no CUDA, no torch); this module is its Python
+face.  Every misuse (no slot left, a slot freed twice, a page held twice)
+raises before anything is launched.
 
 Reference: src/models/turbo_generic.rs:1606-1618 keeps one growing (K, V)
 pair per layer for a single sequence and src/engine.rs:117 one `position`;
@@ -10,186 +13,232 @@ reset) that a slot offers here per sequence.
 """
 from __future__ import annotations
 
+import ctypes
+from ctypes import c_char_p, c_int, c_void_p
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+from ..csrc import build as _build
+
 
 class CacheError(RuntimeError):
     """The cache cannot serve a request (capacity) or was misused."""
 
 
-class IndexPool:
-    """A pool of integer handles 0..n-1 (slots, or pages of one group).
-    Handles are given out lowest first, so that a handle given back is used
-    again soon — stale contents then show up in tests rather than in use."""
-
-    def __init__(self, n: int, what: str):
-        self.n = int(n)
-        self.what = what
-        self._free = list(range(self.n - 1, -1, -1))   # pop() yields the lowest
-        self._held = [False] * self.n
-
-    @property
-    def free_count(self) -> int:
-        return len(self._free)
-
-    @property
-    def held_count(self) -> int:
-        return self.n - len(self._free)
-
-    def take(self) -> int:
-        if not self._free:
-            raise CacheError(f"no free {self.what} left (all {self.n} are held)")
-        i = self._free.pop()
-        if self._held[i]:
-            raise CacheError(f"{self.what} {i} would be held twice")
-        self._held[i] = True
-        return i
-
-    def give_back(self, i: int) -> None:
-        if not 0 <= i < self.n:
-            raise CacheError(f"{self.what} {i} does not exist (0..{self.n - 1})")
-        if not self._held[i]:
-            raise CacheError(f"{self.what} {i} is freed twice or was never held")
-        self._held[i] = False
-        # keep the free list sorted descending so that take() stays lowest-first
-        lo, hi = 0, len(self._free)
-        while lo < hi:
-            mid = (lo + hi) // 2
-            if self._free[mid] > i:
-                lo = mid + 1
-            else:
-                hi = mid
-        self._free.insert(lo, i)
-
-    def is_held(self, i: int) -> bool:
-        return 0 <= i < self.n and self._held[i]
-
-    def check(self) -> None:
-        """Invariant: every handle is either free or held, never both or neither."""
-        free = set(self._free)
-        if len(free) != len(self._free):
-            raise CacheError(f"a {self.what} is on the free list twice")
-        for i in range(self.n):
-            if (i in free) == self._held[i]:
-                raise CacheError(f"{self.what} {i} is {'both free and held' if self._held[i] else 'lost'}")
+class StepError(ValueError):
+    """A step that cannot run; raised before anything is launched."""
 
 
-class GroupPages:
+@dataclass(frozen=True)
+class PageGroup:
     """Pages of one group of layers.  A sequence's logical page i (tokens
-    i*page_tokens ..) lives in physical page `pages[slot][i]`; a ring group
-    holds at most `ring_pages` pages per sequence and reuses them modulo."""
-
-    def __init__(self, name: str, n_pages: int, page_tokens: int, ring_pages: int | None):
-        self.name = name
-        self.page_tokens = page_tokens
-        self.ring_pages = ring_pages
-        self.pool = IndexPool(n_pages, f"page of cache group '{name}'")
-        self.pages: dict[int, list[int]] = {}
+    i*page_tokens ..) lives in one physical page of the group; a ring group
+    (`ring_pages` set) holds at most that many pages per sequence and reuses
+    them modulo."""
+    name: str
+    n_pages: int
+    page_tokens: int
+    ring_pages: Optional[int] = None
 
     def pages_for_length(self, length: int) -> int:
         n = -(-length // self.page_tokens)
         return n if self.ring_pages is None else min(n, self.ring_pages)
 
-    def need(self, slot: int, new_length: int) -> int:
-        n = -(-new_length // self.page_tokens)
-        if self.ring_pages is not None and n > self.ring_pages:
-            n = self.ring_pages
-        have = self.pages.get(slot)
-        n -= len(have) if have is not None else 0
-        return n if n > 0 else 0
 
-    def grow(self, slot: int, new_length: int) -> None:
-        have = self.pages.setdefault(slot, [])
-        for _ in range(self.need(slot, new_length)):
-            have.append(self.pool.take())
+_SIGNATURES = {
+    "tqh_book_new": ([c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p], c_void_p),
+    "tqh_book_delete": ([c_void_p], None),
+    "tqh_error": ([c_void_p], c_char_p),
+    "tqh_alloc": ([c_void_p], c_int),
+    "tqh_free": ([c_void_p, c_int], c_int),
+    "tqh_reserve": ([c_void_p, c_int, c_void_p, c_void_p], c_int),
+    "tqh_commit": ([c_void_p, c_int, c_void_p, c_void_p], c_int),
+    "tqh_trim": ([c_void_p, c_int, c_void_p], c_int),
+    "tqh_length": ([c_void_p, c_int], c_int),
+    "tqh_lengths": ([c_void_p, c_int, c_void_p, c_void_p], c_int),
+    "tqh_is_held": ([c_void_p, c_int], c_int),
+    "tqh_free_slots": ([c_void_p], c_int),
+    "tqh_free_pages": ([c_void_p, c_int], c_int),
+    "tqh_total_pages": ([c_void_p, c_int], c_int),
+    "tqh_page_count": ([c_void_p, c_int, c_int], c_int),
+    "tqh_pages": ([c_void_p, c_int, c_int, c_void_p, c_int], c_int),
+    "tqh_check": ([c_void_p], c_int),
+    "tqh_begin_step": ([c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int], c_int),
+    "tqh_step_layout": ([c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p], c_int),
+    "tqh_pack_step": ([c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_int, c_void_p], c_int),
+    "tqh_pack_decode": ([c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p], c_int),
+}
+_lib = None
 
-    def release(self, slot: int) -> None:
-        for p in self.pages.pop(slot, []):
-            self.pool.give_back(p)
+
+def host_library() -> ctypes.CDLL:
+    """The host runtime, built at first use (a C++ compiler is all it needs)."""
+    global _lib
+    if _lib is None:
+        lib = _build.load("host")
+        for name, (argtypes, restype) in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes, fn.restype = argtypes, restype
+        _lib = lib
+    return _lib
+
+
+def _ints(values) -> np.ndarray:
+    """A contiguous int32 array of `values` (kept by the caller while the C side reads it)."""
+    if isinstance(values, np.ndarray) and values.dtype == np.int32 and values.flags.c_contiguous:
+        return values
+    return np.ascontiguousarray(values, dtype=np.int32)
+
+
+class StepLayout:
+    """Where the segments of a packed step lie in its int32 buffer (see `SlotBook.step_layout`)."""
+    __slots__ = ("offs", "widths", "total")
+
+    def __init__(self, offs: np.ndarray, widths: np.ndarray, total: int):
+        self.offs, self.widths, self.total = offs, widths, total
 
 
 class SlotBook:
     """Slots, lengths and page lists of all groups together.  `reserve` is
     all-or-nothing: it checks every group's pool before it takes a page."""
 
-    def __init__(self, max_slots: int, groups: list[GroupPages], max_length: int):
-        self.slots = IndexPool(max_slots, "slot")
-        self.groups = groups
-        self.max_length = max_length
-        self.length: dict[int, int] = {}
+    def __init__(self, max_slots: int, groups: Sequence[PageGroup], max_length: int):
+        self._lib = host_library()
+        self.groups = list(groups)
+        self.max_slots, self.max_length = int(max_slots), int(max_length)
+        n = len(self.groups)
+        names = (c_char_p * max(n, 1))(*[g.name.encode() for g in self.groups])
+        pages = _ints([g.n_pages for g in self.groups] or [0])           # (locals: alive while the C side reads them)
+        tokens = _ints([g.page_tokens for g in self.groups] or [0])
+        rings = _ints([g.ring_pages or 0 for g in self.groups] or [0])
+        self._h = self._lib.tqh_book_new(self.max_slots, self.max_length, n, pages.ctypes.data, tokens.ctypes.data,
+                                         rings.ctypes.data, ctypes.cast(names, c_void_p))
+        if not self._h:
+            raise CacheError("cache sizes must be positive")
 
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.tqh_book_delete(h)
+
+    def _raise(self, code: int):
+        msg = self._lib.tqh_error(self._h).decode()
+        raise (StepError if code == -2 else CacheError)(msg)
+
+    # ---- slots ----------------------------------------------------------------
     def alloc(self) -> int:
-        s = self.slots.take()
-        self.length[s] = 0
+        s = self._lib.tqh_alloc(self._h)
+        if s < 0:
+            self._raise(s)
         return s
 
     def free(self, slot: int) -> None:
-        self.slots.give_back(slot)       # raises on a double free before any page moves
-        for g in self.groups:
-            g.release(slot)
-        del self.length[slot]
+        r = self._lib.tqh_free(self._h, int(slot))
+        if r:
+            self._raise(r)
 
-    def reserve(self, slots: list[int], new_tokens: list[int]) -> None:
+    def is_held(self, slot: int) -> bool:
+        return bool(self._lib.tqh_is_held(self._h, int(slot)))
+
+    def length(self, slot: int) -> int:
+        n = self._lib.tqh_length(self._h, int(slot))
+        if n < 0:
+            raise CacheError(f"slot {slot} is not held")
+        return n
+
+    def lengths(self, slots) -> list[int]:
+        """The lengths of several slots (-1 for one that is not held)."""
+        s = _ints(slots)
+        out = np.empty(max(len(s), 1), dtype=np.int32)
+        self._lib.tqh_lengths(self._h, len(s), s.ctypes.data, out.ctypes.data)
+        return out[:len(s)].tolist()
+
+    @property
+    def free_slots(self) -> int:
+        return self._lib.tqh_free_slots(self._h)
+
+    # ---- pages ----------------------------------------------------------------
+    def reserve(self, slots, new_tokens) -> None:
         """Pages for `new_tokens[i]` more tokens in `slots[i]`, for all rows or none."""
-        if len(set(slots)) != len(slots):
-            raise CacheError(f"a slot is named twice in one step: {slots}")
-        for s, n in zip(slots, new_tokens):
-            if not self.slots.is_held(s):
-                raise CacheError(f"slot {s} is not held")
-            if n <= 0:
-                raise CacheError(f"slot {s}: a step must bring at least one token")
-            if self.length[s] + n > self.max_length:
-                raise CacheError(
-                    f"slot {s}: {self.length[s]} cached + {n} new tokens exceed the context limit {self.max_length}")
-        # pages each row needs in each group, counted once (a decode step of many rows passes here every token)
-        new_lengths = [self.length[s] + n for s, n in zip(slots, new_tokens)]
-        needs = []
-        for g in self.groups:
-            row = [g.need(s, length) for s, length in zip(slots, new_lengths)]
-            want = sum(row)
-            if want > g.pool.free_count:
-                raise CacheError(
-                    f"cache group '{g.name}' is full: the step needs {want} more pages of {g.page_tokens} tokens, "
-                    f"{g.pool.free_count} of {g.pool.n} are free")
-            needs.append(row if want else None)
-        for g, row in zip(self.groups, needs):
-            if row is None:
-                continue
-            for s, k in zip(slots, row):
-                if k:
-                    have = g.pages.setdefault(s, [])
-                    for _ in range(k):
-                        have.append(g.pool.take())
+        s, n = _ints(slots), _ints(new_tokens)
+        r = self._lib.tqh_reserve(self._h, len(s), s.ctypes.data, n.ctypes.data)
+        if r:
+            self._raise(r)
 
-    def commit(self, slots: list[int], new_tokens: list[int]) -> None:
-        for s, n in zip(slots, new_tokens):
-            self.length[s] += n
+    def commit(self, slots, new_tokens) -> None:
+        s, n = _ints(slots), _ints(new_tokens)
+        self._lib.tqh_commit(self._h, len(s), s.ctypes.data, n.ctypes.data)
 
-    def trim(self, slots: list[int]) -> None:
+    def trim(self, slots) -> None:
         """Gives back the pages of `slots` beyond what their committed lengths
         need (pages reserved for a step that did not happen)."""
-        for s in slots:
-            if not self.slots.is_held(s):
-                continue
-            for g in self.groups:
-                have = g.pages.get(s)
-                if have is None:
-                    continue
-                keep = g.pages_for_length(self.length[s])
-                if len(have) > keep:
-                    for p in have[keep:]:
-                        g.pool.give_back(p)
-                    g.pages[s] = have[:keep]       # a new list: whoever remembers the old one sees the change
+        s = _ints(slots)
+        r = self._lib.tqh_trim(self._h, len(s), s.ctypes.data)
+        if r:
+            self._raise(r)
+
+    def free_pages(self, group: int) -> int:
+        return self._lib.tqh_free_pages(self._h, group)
+
+    def total_pages(self, group: int) -> int:
+        return self._lib.tqh_total_pages(self._h, group)
+
+    def pages(self, group: int, slot: int) -> list[int]:
+        """The slot's physical pages in `group`, in logical order."""
+        n = self._lib.tqh_page_count(self._h, group, int(slot))
+        out = np.empty(max(n, 1), dtype=np.int32)
+        self._lib.tqh_pages(self._h, group, int(slot), out.ctypes.data, n)
+        return out[:n].tolist()
 
     def check(self) -> None:
-        self.slots.check()
-        for g in self.groups:
-            g.pool.check()
-            seen: set[int] = set()
-            for s, pages in g.pages.items():
-                if not self.slots.is_held(s):
-                    raise CacheError(f"group '{g.name}' keeps pages for slot {s}, which is not held")
-                for p in pages:
-                    if p in seen or not g.pool.is_held(p):
-                        raise CacheError(f"group '{g.name}': page {p} is held twice or not marked held")
-                    seen.add(p)
-            if len(seen) != g.pool.held_count:
-                raise CacheError(f"group '{g.name}': {g.pool.held_count - len(seen)} pages are lost")
+        """Invariants: every slot and page is either free or held, never both
+        or neither; a page is held once, by a slot that is held; every sequence
+        has the pages its length needs."""
+        r = self._lib.tqh_check(self._h)
+        if r:
+            self._raise(r)
+
+    # ---- a step's rows ----------------------------------------------------------
+    # Rows are given flat: lens[i] tokens of row i follow one another in `tokens`, want_counts[i] places in
+    # `want`; sources[i] >= 0 names the row of the sampler's ids on the device that holds row i's one token.
+    def begin_step(self, slots, lens, tokens, want_counts, want, sources, vocab: int, source_rows: int) -> None:
+        """The checks of a step that need no device (raises StepError), nothing is changed."""
+        s, n, t, wc, w = _ints(slots), _ints(lens), _ints(tokens), _ints(want_counts), _ints(want)
+        src = _ints(sources) if sources is not None else None
+        r = self._lib.tqh_begin_step(self._h, len(s), s.ctypes.data, n.ctypes.data, t.ctypes.data, wc.ctypes.data,
+                                     w.ctypes.data, src.ctypes.data if src is not None else None, int(vocab),
+                                     int(source_rows))
+        if r:
+            self._raise(r)
+
+    def step_layout(self, slots, lens, want_counts) -> StepLayout:
+        """Offsets of tokens | tok_seq | tok_pos | cu_seqlens | slots | start_pos | new_lens | logit_rows |
+        tok_src | one block table per group in the packed buffer, the tables' widths, the buffer's length."""
+        s, n, wc = _ints(slots), _ints(lens), _ints(want_counts)
+        offs = np.empty(9 + len(self.groups), dtype=np.int32)
+        widths = np.empty(max(len(self.groups), 1), dtype=np.int32)
+        total = self._lib.tqh_step_layout(self._h, len(s), s.ctypes.data, n.ctypes.data, wc.ctypes.data,
+                                          offs.ctypes.data, widths.ctypes.data)
+        return StepLayout(offs, widths, total)
+
+    def pack_step(self, slots, lens, tokens, want_counts, want, sources, layout: StepLayout, buf: np.ndarray) -> None:
+        """Fills `buf` (int32, `layout.total` words) for rows whose pages are reserved."""
+        s, n, t, wc, w = _ints(slots), _ints(lens), _ints(tokens), _ints(want_counts), _ints(want)
+        src = _ints(sources) if sources is not None else None
+        r = self._lib.tqh_pack_step(self._h, len(s), s.ctypes.data, n.ctypes.data, t.ctypes.data, wc.ctypes.data,
+                                    w.ctypes.data, src.ctypes.data if src is not None else None,
+                                    layout.offs.ctypes.data, layout.widths.ctypes.data, layout.total, buf.ctypes.data)
+        if r:
+            self._raise(r)
+
+    def pack_decode(self, slots: np.ndarray, tokens: np.ndarray, sources: np.ndarray, offs: np.ndarray,
+                    widths: np.ndarray, buf_address: int) -> None:
+        """What changes from one decode step to the next (tokens, sources, positions, slots, lengths, block
+        tables) of B one-token rows, written into a buffer of fixed layout at `buf_address`."""
+        r = self._lib.tqh_pack_decode(self._h, len(slots), slots.ctypes.data, tokens.ctypes.data, sources.ctypes.data,
+                                      offs.ctypes.data, widths.ctypes.data, buf_address)
+        if r:
+            self._raise(r)

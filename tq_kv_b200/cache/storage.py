@@ -17,7 +17,7 @@ from typing import Optional
 
 import torch
 
-from .pool import CacheError, GroupPages, SlotBook
+from .pool import CacheError, PageGroup, SlotBook
 
 PAGE_TOKENS = 64
 
@@ -74,7 +74,7 @@ class KVGroup:
         ring = None
         if request.window is not None:
             ring = ring_pages_for(request.window, window_slack)
-        self.book = GroupPages(name, n_pages, PAGE_TOKENS, ring)
+        self.book = PageGroup(name, n_pages, PAGE_TOKENS, ring)     # the group's geometry; the engine's SlotBook keeps its pages
         shape = (len(entries), n_pages, request.n_kv_heads, PAGE_TOKENS)
         self.k = torch.zeros((*shape, request.head_dim), dtype=dtype, device=device)
         self.v = torch.zeros((*shape, request.value_dim or request.head_dim), dtype=dtype, device=device)
@@ -137,11 +137,11 @@ class SequenceCache:
         self.book.free(slot)
 
     def length(self, slot: int) -> int:
-        return self.book.length[slot]
+        return self.book.length(slot)
 
     @property
     def free_slots(self) -> int:
-        return self.book.slots.free_count
+        return self.book.free_slots
 
     # ---- one step ----------------------------------------------------------
     def reserve(self, slots: list[int], new_tokens: list[int]) -> None:
@@ -155,8 +155,7 @@ class SequenceCache:
 
     def block_table_rows(self, group: int, slots: list[int]) -> tuple[list[list[int]], int]:
         """The page lists of `slots` in group `group` and the widest of them."""
-        pages = self.groups[group].book.pages
-        rows = [pages.get(s, []) for s in slots]
+        rows = [self.book.pages(group, s) for s in slots]
         return rows, max((len(r) for r in rows), default=0)
 
     def layer_pages(self, entry: int) -> tuple[int, torch.Tensor, torch.Tensor]:
@@ -167,10 +166,10 @@ class SequenceCache:
     def free_pages(self) -> int:
         """Pages a new sequence can still get: the scarcest all-keys group
         decides (a window group never needs more pages than those)."""
-        full = [g.book.pool.free_count for g in self.groups if g.book.ring_pages is None]
+        full = [self.book.free_pages(gi) for gi, g in enumerate(self.groups) if g.book.ring_pages is None]
         if full:
             return min(full)
-        return min((g.book.pool.free_count for g in self.groups), default=1 << 30)
+        return min((self.book.free_pages(gi) for gi in range(len(self.groups))), default=1 << 30)
 
     def bytes(self) -> int:
         return sum(g.bytes() for g in self.groups) + sum(t.numel() * t.element_size() for t in self.state.values())

@@ -1,7 +1,8 @@
-"""Builds the CUDA libraries of this package with nvcc for sm_100a and loads
-them with ctypes.
+"""Builds the native libraries of this package and loads them with ctypes: the
+CUDA kernels with nvcc for sm_100a, the host runtime (plain C++, no CUDA) with
+the system's C++ compiler.
 
-A library is a named group of .cu files of this folder.  The shared object is
+A library is a named group of .cu (or .cpp) files of this folder.  The shared object is
 written beside the sources as `_build/libtqkv_<group>_<hash>.so`, where the
 hash covers the sources, the headers and the flags, so that a stale build is
 never loaded.  If the folder cannot be written to, a per-user folder under
@@ -29,12 +30,16 @@ GROUPS: dict[str, list[str]] = {
              "gemm_tc.cu", "decode_gemm_tc.cu", "sampling.cu", "random_fill.cu"],
     # decode attention for callers that cannot allocate: a library of its own (flash_decode_static.h)
     "noalloc": ["flash_decode_static.cu"],
+    # the host side of a step: cache bookkeeping, checks and packing (C++, no CUDA: builds and runs without a GPU)
+    "host": ["host_runtime.cpp"],
 }
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
 ]
+
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -56,13 +61,26 @@ def find_nvcc() -> str:
                      "the CUDA kernels of this package cannot be built")
 
 
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    raise BuildError("no C++ compiler was found (looked at $CXX, g++, c++, clang++); "
+                     "the host runtime of this package cannot be built")
+
+
+def _is_host(group: str) -> bool:
+    return all(src.endswith(".cpp") for src in GROUPS[group])
+
+
 def _headers() -> list[str]:
     return sorted(f for f in os.listdir(_HERE) if f.endswith((".cuh", ".h")))
 
 
 def group_hash(group: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(HOST_FLAGS if _is_host(group) else NVCC_FLAGS).encode())
     included = sorted(f for f in os.listdir(_HERE) if f.endswith(".cu") and f not in GROUPS[group]
                       and any(f'#include "{f}"' in open(os.path.join(_HERE, src)).read() for src in GROUPS[group]))
     for name in GROUPS[group] + included + _headers():
@@ -114,6 +132,8 @@ def build(group: str, verbose_ptxas: bool = False) -> str:
     have = library_path(group)
     if have:
         return have
+    if _is_host(group):
+        return _build_host(group)
     nvcc = find_nvcc()
     out_dir = _writable_build_dir()
     tag = group_hash(group)
@@ -149,6 +169,29 @@ def build(group: str, verbose_ptxas: bool = False) -> str:
     finally:
         shutil.rmtree(work, ignore_errors=True)
     _say(f"built {os.path.basename(final)} in {time.time() - t0:.0f} s")
+    return final
+
+
+def _build_host(group: str) -> str:
+    cxx = find_cxx()
+    out_dir = _writable_build_dir()
+    final = os.path.join(out_dir, f"libtqkv_{group}_{group_hash(group)}.so")
+    tmp_so = os.path.join(out_dir, f".{os.path.basename(final)}.{os.getpid()}")
+    t0 = time.time()
+    try:
+        _run([cxx, *HOST_FLAGS, "-shared", "-I", _HERE, "-o", tmp_so, *(os.path.join(_HERE, s) for s in GROUPS[group])],
+             f"{os.path.basename(cxx)} {group}")
+        os.replace(tmp_so, final)
+    finally:
+        if os.path.exists(tmp_so):
+            os.remove(tmp_so)
+    for old in os.listdir(out_dir):
+        if old.startswith(f"libtqkv_{group}_") and old.endswith(".so") and old != os.path.basename(final):
+            try:
+                os.remove(os.path.join(out_dir, old))
+            except OSError:
+                pass
+    _say(f"built {os.path.basename(final)} in {time.time() - t0:.1f} s")
     return final
 
 

@@ -28,57 +28,46 @@ def _pad4(n: int) -> int:
     return (n + 3) // 4 * 4
 
 
-def build_step_batch(rows: list[StepRow], cache: SequenceCache, device) -> StepBatch:
-    """Packs `rows` (already reserved in the cache).  Layout of the buffer:
-    tokens | tok_seq | tok_pos | cu_seqlens | slots | start_pos | new_lens |
-    logit_rows | tok_src | one block table per cache group; every segment
-    starts on a 16-byte boundary."""
+class FlatRows:
+    """The rows of a step as the host runtime takes them: flat int32 arrays."""
+    __slots__ = ("slots", "lens", "tokens", "want_counts", "want", "sources", "any_source")
+
+    def __init__(self, rows: list[StepRow]):
+        self.slots = np.fromiter((r.slot for r in rows), dtype=np.int32, count=len(rows))
+        self.lens = np.fromiter((len(r.tokens) for r in rows), dtype=np.int32, count=len(rows))
+        self.want_counts = np.fromiter((len(r.want) for r in rows), dtype=np.int32, count=len(rows))
+        if len(rows) == 1:
+            self.tokens = np.asarray(rows[0].tokens, dtype=np.int64)
+            self.want = np.asarray(rows[0].want, dtype=np.int64)
+        else:
+            self.tokens = np.concatenate([np.asarray(r.tokens, dtype=np.int64) for r in rows])
+            self.want = np.concatenate([np.asarray(r.want, dtype=np.int64) for r in rows])
+        # ids and places that do not fit 32 bits are out of every range: they become -1, which every check refuses
+        self.tokens = np.where((self.tokens >= 0) & (self.tokens < 2 ** 31), self.tokens, -1).astype(np.int32)
+        self.want = np.where((self.want >= 0) & (self.want < 2 ** 31), self.want, -1).astype(np.int32)
+        self.any_source = any(r.source is not None for r in rows)
+        self.sources = np.fromiter((-1 if r.source is None else r.source for r in rows), dtype=np.int32,
+                                   count=len(rows))
+
+
+def build_step_batch(rows: list[StepRow], cache: SequenceCache, device, flat: Optional[FlatRows] = None) -> StepBatch:
+    """Packs `rows` (already reserved in the cache) into one pinned int32
+    buffer and copies it to the device.  The host runtime lays the buffer out
+    (csrc/host_runtime.cpp): tokens | tok_seq | tok_pos | cu_seqlens | slots |
+    start_pos | new_lens | logit_rows | tok_src | one block table per cache
+    group; every segment starts on a 16-byte boundary."""
+    flat = flat or FlatRows(rows)
+    book = cache.book
     B = len(rows)
-    lens = [len(r.tokens) for r in rows]
-    T = sum(lens)
-    starts = [cache.length(r.slot) for r in rows]
-    slots = [r.slot for r in rows]
-    R = sum(len(r.want) for r in rows)
-    tables = [cache.block_table_rows(gi, slots) for gi in range(len(cache.groups))]
-
-    seg_sizes = [T, T, T, B + 1, B, B, B, R, T] + [B * max(w, 1) for _, w in tables]
-    offs, total = [], 0
-    for s in seg_sizes:
-        offs.append(total)
-        total += _pad4(max(s, 1))
-    buf = np.zeros(total, dtype=np.int32)
-
-    cu = np.zeros(B + 1, dtype=np.int64)
-    cu[1:] = np.cumsum(lens)
-    for b, r in enumerate(rows):
-        a, e = int(cu[b]), int(cu[b + 1])
-        buf[offs[0] + a: offs[0] + e] = r.tokens
-        buf[offs[1] + a: offs[1] + e] = b
-        buf[offs[2] + a: offs[2] + e] = np.arange(starts[b], starts[b] + lens[b])
-    buf[offs[3]: offs[3] + B + 1] = cu
-    buf[offs[4]: offs[4] + B] = slots
-    buf[offs[5]: offs[5] + B] = starts
-    buf[offs[6]: offs[6] + B] = [s + n for s, n in zip(starts, lens)]
-    o = offs[7]
-    for b, r in enumerate(rows):
-        for w in r.want:
-            buf[o] = int(cu[b]) + w
-            o += 1
-    buf[offs[8]: offs[8] + T] = -1
-    for b, r in enumerate(rows):
-        if r.source is not None:
-            buf[offs[8] + int(cu[b])] = r.source
-    for gi, (trows, width) in enumerate(tables):
-        w = max(width, 1)
-        base = offs[9 + gi]
-        for b, pages in enumerate(trows):
-            buf[base + b * w: base + b * w + len(pages)] = pages
-
-    host = torch.from_numpy(buf)
+    T, R = int(flat.lens.sum()), int(flat.want_counts.sum())
+    starts = book.lengths(flat.slots)
+    layout = book.step_layout(flat.slots, flat.lens, flat.want_counts)
     dev = torch.device(device)
-    if dev.type == "cuda":
-        host = host.pin_memory()
+    host = torch.empty(layout.total, dtype=torch.int32, pin_memory=dev.type == "cuda")
+    book.pack_step(flat.slots, flat.lens, flat.tokens, flat.want_counts, flat.want, flat.sources, layout, host.numpy())
     d = host.to(dev, non_blocking=True)
+    offs = layout.offs.tolist()
+    widths = layout.widths.tolist()
 
     def seg(i: int, n: int) -> torch.Tensor:
         return d[offs[i]: offs[i] + n]
@@ -86,6 +75,6 @@ def build_step_batch(rows: list[StepRow], cache: SequenceCache, device) -> StepB
     return StepBatch(
         n_tokens=T, n_seqs=B, tokens=seg(0, T), tok_seq=seg(1, T), tok_pos=seg(2, T), cu_seqlens=seg(3, B + 1),
         slots=seg(4, B), start_pos=seg(5, B), new_lens=seg(6, B), logit_rows=seg(7, R), n_logit_rows=R,
-        block_tables=[(seg(9 + gi, B * max(w, 1)), max(w, 1)) for gi, (_, w) in enumerate(tables)],
-        host_slots=slots, host_start=starts, host_lens=lens, packed_bytes=int(buf.nbytes), tok_src=seg(8, T),
-        any_source=any(r.source is not None for r in rows))
+        block_tables=[(seg(9 + gi, B * widths[gi]), widths[gi]) for gi in range(len(cache.groups))],
+        host_slots=flat.slots.tolist(), host_start=starts, host_lens=flat.lens.tolist(),
+        packed_bytes=layout.total * 4, tok_src=seg(8, T), any_source=flat.any_source)

@@ -78,8 +78,12 @@ class DecodeGraph:
         self.graph = None
         self.logits = None
         self.kernels_per_replay = 0
-        self._tables = [np.zeros((B, w), dtype=np.int32) for w in self.widths]      # see _fill
-        self._seen = [[(None, -1)] * B for _ in self.widths]
+        # what the host runtime fills per step (csrc/host_runtime.cpp, tqh_pack_decode), and where
+        self._offs = np.asarray(self.offs, dtype=np.int32)
+        self._widths = np.asarray(self.widths or [1], dtype=np.int32)
+        self._slots = np.zeros(B, dtype=np.int32)
+        self._tokens = np.zeros(B, dtype=np.int32)
+        self._sources = np.zeros(B, dtype=np.int32)
 
     def _fill(self, rows) -> torch.Tensor:
         i = self.turn % self.RING
@@ -87,28 +91,12 @@ class DecodeGraph:
         if self.events[i] is not None:
             self.events[i].synchronize()                      # the copy that last used this buffer is done
         h = self.host[i]
-        a = h.numpy()
-        o, B, cache = self.offs, self.B, self.cache
         slots = [r.slot for r in rows]
-        starts = [cache.length(s) for s in slots]
-        a[o[0]:o[0] + B] = [r.tokens[0] for r in rows]
-        a[o[8]:o[8] + B] = [-1 if r.source is None else r.source for r in rows]
-        a[o[2]:o[2] + B] = starts
-        a[o[4]:o[4] + B] = slots
-        a[o[5]:o[5] + B] = starts
-        a[o[6]:o[6] + B] = [s + 1 for s in starts]
-        # Block tables: a row changes only when its sequence gets a page or the slot gets another sequence, so
-        # the rows are kept on the host and only those whose page list (the object or its length) is another
-        # than last time are rewritten; the whole table then goes into the staging buffer in one copy.
-        for gi, w in enumerate(self.widths):
-            trows, _ = cache.block_table_rows(gi, slots)
-            table, seen = self._tables[gi], self._seen[gi]
-            for b, pages in enumerate(trows):
-                last = seen[b]
-                if last[0] is not pages or last[1] != len(pages):
-                    table[b, :len(pages)] = pages
-                    seen[b] = (pages, len(pages))
-            a[o[9 + gi]:o[9 + gi] + B * w] = table.reshape(-1)
+        self._slots[:] = slots
+        self._tokens[:] = [r.tokens[0] for r in rows]
+        self._sources[:] = [-1 if r.source is None else r.source for r in rows]
+        # tokens, sources, positions, slots, lengths and the block tables, written by the host runtime in one call
+        self.cache.book.pack_decode(self._slots, self._tokens, self._sources, self._offs, self._widths, h.data_ptr())
         self.batch.host_slots = slots
         self.dev.copy_(h, non_blocking=True)
         ev = torch.cuda.Event()

@@ -17,22 +17,18 @@ from typing import Optional, Sequence
 import torch
 
 from .. import kernels
-from ..cache import PAGE_TOKENS, CacheError, SequenceCache
+from ..cache import PAGE_TOKENS, CacheError, SequenceCache, StepError
 from ..config import read_config_json, spec_from_config_dict
 from ..parts import Runtime
 from ..weights import load_tensors, random_tensors
 from ..weights.random_init import storage_dtype
-from .batch import StepRow, build_step_batch
+from .batch import FlatRows, StepRow, build_step_batch
 from .decode_graph import DecodeGraph, forward_step
 from .readback import SampledIds
 from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
-
-
-class StepError(ValueError):
-    """A step that cannot run; raised before anything is launched."""
 
 
 def _round_up(n: int, m: int) -> int:
@@ -153,33 +149,23 @@ class Engine:
         rows = list(rows)
         if not rows:
             raise StepError("a step needs at least one row")
-        V = self.vocab_size
-        for r in rows:
-            if not r.tokens:
-                raise StepError(f"slot {r.slot}: Empty prompt")          # src/engine.rs:347-349
-            if r.source is not None:
-                if len(r.tokens) != 1 or not 0 <= r.source < self.sampled.rows:
-                    raise StepError(f"slot {r.slot}: a row fed from the sampler brings exactly one token")
-            else:
-                bad = [t for t in r.tokens if not 0 <= int(t) < V]
-                if bad:
-                    raise StepError(f"slot {r.slot}: token id {bad[0]} is outside the vocabulary (0..{V - 1})")
-            for w in r.want:
-                if not 0 <= w < len(r.tokens):
-                    raise StepError(f"slot {r.slot}: wanted place {w} is outside the {len(r.tokens)} tokens brought")
-        slots = [r.slot for r in rows]
-        lens = [len(r.tokens) for r in rows]
-        for s in slots:
-            if not self.cache.book.slots.is_held(s):
-                raise StepError(f"slot {s} is not held")
-        self.model.check_step([self.cache.length(s) for s in slots], lens)
         try:
-            self.cache.reserve(slots, lens)
+            flat = FlatRows(rows)
+        except (OverflowError, TypeError, ValueError) as e:
+            raise StepError(f"a row's slot, tokens or wanted places are not 32-bit integers: {e}") from e
+        # the checks that need no device, then the pages (all rows or none): the host runtime does both
+        book = self.cache.book
+        book.begin_step(flat.slots, flat.lens, flat.tokens, flat.want_counts, flat.want, flat.sources,
+                        self.vocab_size, self.sampled.rows)
+        slots, lens = flat.slots, flat.lens
+        self.model.check_step(book.lengths(slots), lens.tolist())
+        try:
+            book.reserve(slots, lens)
         except CacheError as e:
             raise StepError(str(e)) from e
         try:
             with torch.cuda.device(self.runtime.device):
-                if self.use_graphs and all(n == 1 for n in lens) and all(r.want == [0] for r in rows):
+                if self.use_graphs and int(lens.max()) == 1 and all(r.want == [0] for r in rows):
                     graph = self._decode_graphs.get(len(rows))
                     if graph is None:
                         graph = self._decode_graphs[len(rows)] = DecodeGraph(
@@ -188,7 +174,7 @@ class Engine:
                     self.h2d_bytes += graph.batch.packed_bytes
                     kernels.mark_tc_launched()      # read with the sampled ids, or by check_status()
                 else:
-                    batch = build_step_batch(rows, self.cache, self.runtime.device)
+                    batch = build_step_batch(rows, self.cache, self.runtime.device, flat)
                     logits = self._forward(batch)
                     self.h2d_bytes += batch.packed_bytes
                     if check:
