@@ -236,6 +236,12 @@ def cmd_doctor() -> int:
     ok = torch.cuda.is_available()
     print(f"CUDA device: {torch.cuda.get_device_name(0) if ok else 'none'}")
     try:
+        print(f"C++ compiler: {build.find_cxx()}")
+        print(f"host runtime: {build.build('host')}")
+    except build.BuildError as e:
+        print(f"host runtime: FAILED\n{e}")
+        ok = False
+    try:
         print(f"nvcc: {build.find_nvcc()}")
         print(f"CUDA library: {build.build('core')}")
     except build.BuildError as e:
