@@ -736,6 +736,26 @@ def test_sample_follows_the_plain_sampler(V, temperature, top_k, top_p):
     assert out.tolist() == want
 
 
+@pytest.mark.parametrize("top_k", [0, 40])
+def test_draws_made_on_the_device_are_the_host_generators(top_k):
+    """With request indices instead of uniforms the kernel generates each row's draw from (seed, request, index
+    of the sampled token): the same tokens as with the host generator's numbers, whatever row a request sits in."""
+    from tq_kv_b200 import kernels
+    from tq_kv_b200.sampling import uniform
+    R, V = 7, 3000
+    logits = rnd(R, V, scale=2.0, seed=11)
+    requests = [12, 0, 5, 1000003, 7, 3, 2 ** 31 - 1]
+    for seed, index in [(0, 0), (1234567890123, 5), (2 ** 64 - 1, 70000)]:
+        us = torch.tensor([uniform(seed, r, index) for r in requests], dtype=torch.float32, device=DEV)
+        want = torch.zeros(R, dtype=torch.int32, device=DEV)
+        kernels.sample(logits, want, temperature=0.9, top_k=top_k, top_p=0.95, uniforms=us)
+        got = torch.zeros(R, dtype=torch.int32, device=DEV)
+        kernels.sample(logits, got, temperature=0.9, top_k=top_k, top_p=0.95, seed=seed, index=index,
+                       requests=torch.tensor(requests, dtype=torch.int32, device=DEV))
+        assert got.tolist() == want.tolist()
+    assert len(set(want.tolist())) > 1
+
+
 def test_argmax_ties_go_to_the_lowest_id():
     from tq_kv_b200 import kernels
     logits = torch.zeros(2, 5000, device=DEV)

@@ -74,10 +74,34 @@ __device__ double block_sum_f64(double v, double* red) {
     return warp_sum_f64(r);
 }
 
+// Where a row's uniform draw in [0, 1) comes from: an array the caller filled, or the counter-based generator
+// of sampling/rng.py run here: a draw depends on (seed, request index, index of the sampled token) only, so a
+// request's output does not depend on what else is in its batch or on the slot it got (the reference seeds one
+// generator per call, src/engine.rs:362).  24 random bits, exact in float32.
+struct Draws {
+    const float* uniforms;           // [rows], or null: generate
+    const int* requests;             // [rows] request index of each row
+    unsigned long long seed;
+    int index;
+};
+__device__ __forceinline__ unsigned long long draw_mix(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ float draw_uniform(const Draws& d, int row) {
+    if (d.uniforms) return d.uniforms[row];
+    unsigned long long z = draw_mix(d.seed);
+    z = draw_mix(z ^ ((unsigned long long)(long long)d.requests[row] * 0xD6E8FEB86659FD93ull));
+    z = draw_mix(z ^ ((unsigned long long)(long long)d.index * 0xA0761D6478BD642Full));
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
 // One block per row.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature, int top_k, float top_p,
-              const float* __restrict__ uniforms, int* __restrict__ counts, float penalty, int* __restrict__ out) {
+              Draws draws, int* __restrict__ counts, float penalty, int* __restrict__ out) {
     __shared__ ArgMax red_am[32];
     __shared__ double red_d[32];
     __shared__ int hist_i[256];
@@ -207,7 +231,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     if (tid == 0) {
         double total = 0.0;
         for (int t = 0; t < (int)blockDim.x; ++t) total += seg_sum[t];
-        const double target = (double)uniforms[row] * total;
+        const double target = (double)draw_uniform(draws, row) * total;
         double cum = 0.0;
         int owner = -1;
         for (int t = 0; t < (int)blockDim.x; ++t) {
@@ -331,7 +355,7 @@ topk_parts_kernel(const float* __restrict__ logits, int ld, int V, const int* __
 __global__ void __launch_bounds__(256)
 topk_final_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_idx,
                   const int* __restrict__ cand_cnt, int V, float temperature, int top_k, float top_p,
-                  const float* __restrict__ uniforms, int* __restrict__ counts, int* __restrict__ out) {
+                  Draws draws, int* __restrict__ counts, int* __restrict__ out) {
     __shared__ uint32_t keys[TOPK_PARTS * TOPK_CAP];             // order keys of the candidates' logits
     __shared__ int idxs[TOPK_PARTS * TOPK_CAP];
     __shared__ float kp[TOPK_KEEP_MAX], sp[TOPK_KEEP_MAX];       // kept probabilities; the same, sorted
@@ -412,7 +436,7 @@ topk_final_kernel(const float* __restrict__ cand_val, const int* __restrict__ ca
     if (tid == 0) {
         double total = 0.0;
         for (int j = 0; j < m; ++j) total += (double)sp[j];
-        const double target = (double)uniforms[row] * total;
+        const double target = (double)draw_uniform(draws, row) * total;
         double cum = 0.0;
         int tok = -1, last = -1;
         for (int j = 0; j < m; ++j) {
@@ -473,12 +497,11 @@ TQ_API size_t tq_sample_scratch_bytes(int n_rows) {
     return (size_t)n_rows * TOPK_PARTS * (TOPK_CAP * 8 + 4) + 256;
 }
 
-TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float temperature, int top_k, float top_p,
-                     const float* uniforms, int* counts, float penalty, int* out, void* scratch,
-                     cudaStream_t stream) {
+static int sample_launch(const float* logits, int ld, int n_rows, int V, float temperature, int top_k, float top_p,
+                         Draws draws, int* counts, float penalty, int* out, void* scratch, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V) return (int)cudaErrorInvalidValue;
-    if (temperature > 0.f && !uniforms) return (int)cudaErrorInvalidValue;
+    if (temperature > 0.f && !draws.uniforms && !draws.requests) return (int)cudaErrorInvalidValue;
     if (counts && !(penalty > 0.f)) return (int)cudaErrorInvalidValue;
     if (temperature <= 0.f && scratch && n_rows <= 65535) {
         int st = tq_launch_pdl(TQ_PDL_SAMPLING, argmax_parts_kernel, dim3(n_rows, ARGMAX_PARTS), dim3(256), 0, stream, logits, ld, V,
@@ -496,9 +519,25 @@ TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float tempe
                                (const int*)counts, penalty, top_k, cand_val, cand_idx, cand_cnt);
         if (st) return st;
         return tq_launch_pdl(TQ_PDL_SAMPLING, topk_final_kernel, dim3(n_rows), dim3(256), 0, stream, (const float*)cand_val,
-                             (const int*)cand_idx, (const int*)cand_cnt, V, temperature, top_k, top_p, uniforms,
+                             (const int*)cand_idx, (const int*)cand_cnt, V, temperature, top_k, top_p, draws,
                              counts, out);
     }
     return tq_launch_pdl(TQ_PDL_SAMPLING, sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
-                         top_k, top_p, uniforms, counts, penalty, out);
+                         top_k, top_p, draws, counts, penalty, out);
+}
+
+TQ_API int tq_sample(const float* logits, int ld, int n_rows, int V, float temperature, int top_k, float top_p,
+                     const float* uniforms, int* counts, float penalty, int* out, void* scratch,
+                     cudaStream_t stream) {
+    return sample_launch(logits, ld, n_rows, V, temperature, top_k, top_p, Draws{uniforms, nullptr, 0ull, 0}, counts,
+                         penalty, out, scratch, stream);
+}
+
+// The same with the rows' draws generated on the device: requests [rows] int32 (the request index of each row),
+// the generation's seed and the index of the token being sampled (see Draws).
+TQ_API int tq_sample_seeded(const float* logits, int ld, int n_rows, int V, float temperature, int top_k, float top_p,
+                            const int* requests, unsigned long long seed, int index, int* counts, float penalty,
+                            int* out, void* scratch, cudaStream_t stream) {
+    return sample_launch(logits, ld, n_rows, V, temperature, top_k, top_p, Draws{nullptr, requests, seed, index}, counts,
+                         penalty, out, scratch, stream);
 }

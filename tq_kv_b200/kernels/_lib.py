@@ -177,6 +177,8 @@ _SIGNATURES = {
     "tq_attention_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p,
                   c_void_p, c_void_p],
+    "tq_sample_seeded": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, ctypes.c_ulonglong, c_int,
+                         c_void_p, c_float, c_void_p, c_void_p, c_void_p],
 }
 
 _core = None

@@ -17,11 +17,9 @@ import torch
 
 from .. import kernels
 from .params import GenerationParams
-from .rng import uniform
 
 
 class Sampler:
-    U_RING = 8
     def __init__(self, params: GenerationParams, n_rows: int, vocab_size: int, device):
         params.validate()
         self.params = params
@@ -34,9 +32,8 @@ class Sampler:
         self.out = torch.zeros(n_rows, dtype=torch.int32, device=self.device)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
-        self._cap = n_rows
-        self._u_host = self._u_dev = self._u_events = None
-        self._u_turn = 0
+        self._requests: Optional[list] = None           # the request index of each row, as the device holds it
+        self._requests_dev = torch.zeros(max(n_rows, 1), dtype=torch.int32, device=self.device)
 
     def keep(self, rows: Sequence[int]) -> None:
         """Keeps the given rows (indices into the current rows), in order."""
@@ -45,31 +42,16 @@ class Sampler:
             idx = torch.tensor(list(rows), dtype=torch.long, device=self.device)
             self.counts = self.counts.index_select(0, idx).contiguous()
 
-    def _uniforms(self, requests: Sequence[int], index: int) -> torch.Tensor:
-        """The rows' draws for sampled token `index`, copied to the device from a
-        small ring of pinned buffers (a buffer is reused only after several later
-        draws, by when the kernel that read it has long run)."""
-        R = len(requests)
-        if self._u_host is None:
-            self._u_host = [torch.zeros(self._cap, dtype=torch.float32).pin_memory()
-                            if self.device.type == "cuda" else torch.zeros(self._cap, dtype=torch.float32)
-                            for _ in range(self.U_RING)]
-            self._u_dev = [torch.zeros(self._cap, dtype=torch.float32, device=self.device)
-                           for _ in range(self.U_RING)]
-            self._u_events = [None] * self.U_RING
-        i = self._u_turn % self.U_RING
-        self._u_turn += 1
-        if self._u_events[i] is not None:
-            self._u_events[i].synchronize()
-        p = self.params
-        self._u_host[i][:R] = torch.tensor([uniform(p.seed, r, index) for r in requests], dtype=torch.float32)
-        self._u_dev[i][:R].copy_(self._u_host[i][:R], non_blocking=True)
-        if self.device.type == "cuda":
-            ev = torch.cuda.Event()
-            ev.record()
-            self._u_events[i] = ev
-        self.h2d_bytes += 4 * R
-        return self._u_dev[i]
+    def _request_rows(self, requests: Sequence[int]) -> torch.Tensor:
+        """The rows' request indices on the device (copied only when the rows change): with the seed and the
+        index of the sampled token they select each row's uniform draw, which the kernel generates itself."""
+        requests = list(requests)
+        if requests != self._requests:
+            R = len(requests)
+            self._requests_dev[:R].copy_(torch.tensor(requests, dtype=torch.int32), non_blocking=False)
+            self._requests = requests
+            self.h2d_bytes += 4 * R
+        return self._requests_dev
 
     def sample_device(self, logits: torch.Tensor, requests: Sequence[int], index: int,
                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -82,10 +64,10 @@ class Sampler:
         if R != self.n_rows or len(requests) != R:
             raise ValueError(f"sampler holds {self.n_rows} rows, got logits for {R}")
         out = self.out if out is None else out
-        uniforms = self._uniforms(requests, index) if p.temperature > 0 else None
+        rows = self._request_rows(requests) if p.temperature > 0 else None
         kernels.sample(logits, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
-                       uniforms=uniforms, counts=self.counts[:R] if self.counts is not None else None,
-                       repeat_penalty=p.repeat_penalty)
+                       requests=rows, seed=p.seed, index=index,
+                       counts=self.counts[:R] if self.counts is not None else None, repeat_penalty=p.repeat_penalty)
         return out
 
     def sample(self, logits: torch.Tensor, requests: Sequence[int], index: int) -> list[int]:
