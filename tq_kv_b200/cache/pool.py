@@ -121,8 +121,12 @@ class SlotBook:
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
-            self._lib.tqh_book_delete(h)
+        lib = getattr(self, "_lib", None)
+        if h and lib is not None:                          # (at interpreter exit the library may be gone already)
+            try:
+                lib.tqh_book_delete(h)
+            except Exception:
+                pass
 
     def _raise(self, code: int):
         msg = self._lib.tqh_error(self._h).decode()
