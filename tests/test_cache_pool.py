@@ -230,3 +230,54 @@ def test_ring_holds_the_window_plus_the_slack():
     c = SequenceCache({0: KVRequest(1, 16, 64)}, {}, max_tokens=1024, max_slots=2, max_length=1024,
                       dtype=torch.float32, device="cpu", window_slack=63)
     assert c.groups[0].ring_pages == 2
+
+
+def test_packed_steps_of_random_rows_equal_a_plain_packing():
+    """The host runtime's packing against the same layout written out in plain Python, for random rows on a
+    book in a random state (several groups, a ring, slots with history)."""
+    rng = random.Random(3)
+    for trial in range(40):
+        groups = [PageGroup("full", 64, PAGE_TOKENS, None)]
+        if trial % 2:
+            groups.append(PageGroup("win", 32, PAGE_TOKENS, rng.randint(1, 3)))
+        b = SlotBook(8, groups, 2000)
+        slots = [b.alloc() for _ in range(rng.randint(1, 8))]
+        for s in slots:                                             # some history
+            n = rng.randint(0, 300)
+            if n:
+                b.reserve([s], [n]); b.commit([s], [n])
+        rows = rng.sample(slots, rng.randint(1, len(slots)))
+        lens = [rng.randint(1, 90) for _ in rows]
+        tokens = [rng.randrange(1000) for _ in range(sum(lens))]
+        wants = [sorted(rng.sample(range(n), rng.randint(0, min(n, 3)))) for n in lens]
+        sources = [rng.randrange(8) if n == 1 and rng.random() < 0.5 else -1 for n in lens]
+        b.begin_step(rows, lens, tokens, [len(w) for w in wants], [x for w in wants for x in w], sources, 1000, 8)
+        b.reserve(rows, lens)
+        lay = b.step_layout(rows, lens, [len(w) for w in wants])
+        buf = np.full(lay.total, -9, dtype=np.int32)
+        b.pack_step(rows, lens, tokens, [len(w) for w in wants], [x for w in wants for x in w], sources, lay, buf)
+        # the same, written out
+        starts = b.lengths(rows)
+        T, B, R = sum(lens), len(rows), sum(len(w) for w in wants)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        widths = [max([len(b.pages(g, s)) for s in rows] + [1]) for g in range(len(groups))]
+        segs = [tokens, [i for i, n in enumerate(lens) for _ in range(n)],
+                [starts[i] + j for i, n in enumerate(lens) for j in range(n)], cu, rows, starts,
+                [s + n for s, n in zip(starts, lens)], [cu[i] + x for i, w in enumerate(wants) for x in w],
+                [sources[i] if j == 0 else -1 for i, n in enumerate(lens) for j in range(n)]]
+        for g, w in enumerate(widths):
+            table = []
+            for s in rows:
+                p = b.pages(g, s)
+                table += p + [0] * (w - len(p))
+            segs.append(table)
+        assert lay.widths.tolist()[:len(groups)] == widths
+        off = 0
+        for i, seg in enumerate(segs):
+            assert lay.offs[i] == off and buf[off:off + len(seg)].tolist() == list(seg), (trial, i)
+            off += (max(len(seg), 1) + 3) // 4 * 4
+        assert lay.total == off and (T, B, R) == (len(segs[0]), len(segs[4]), len(segs[7]))
+        b.commit(rows, lens)
+        b.check()
