@@ -16,7 +16,7 @@
 // gating, adding into the float32 residual stream, float32 or bfloat16 out.
 //
 // Float32 results without gating have a second way to split K (REDUCE): the
-// shares are independent blocks, as many as fill the GPU twice, and each hands
+// shares are independent blocks, as many as fill the GPU's block slots (two an SM) once, and each hands
 // its partial tile to TMA as a reduce-add, which sums in the L2
 // (cp.reduce.async.bulk.tensor); a result that is not added to the residual
 // stream is cleared first.  No cluster, no exchange through shared memory;
