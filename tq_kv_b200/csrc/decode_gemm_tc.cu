@@ -1,4 +1,4 @@
-// Weight-streaming product for decoding batches of 17..64 rows on the
+// Weight-streaming product for decoding batches of up to 64 rows on the
 // tcgen05 tensor cores, operands swapped: the 128 rows of a W tile are the
 // "M" side of the instruction, the (padded) batch is its "N" side, so the
 // accumulator D[128 weight rows x batch] sits in TMEM with one weight row per
