@@ -15,7 +15,8 @@ run has them (`e2e.steps`, `e2e.warmup`).  `prefill`
 is one step over a 2,048-token prompt; `roofline` relates the decode step's
 necessary bytes (every weight it uses once, the cache of the live sequences)
 to its time; `points` hold decode at batch 1 and 64, device-timed and end to
-end; `kernels` holds the device time of one decode step and of the prefill by
+end, and the time to the first token of a 32- and a 2,048-token prompt through
+`Engine.generate()` (`ttft_ms_p32`, `ttft_ms_p2048`); `kernels` holds the device time of one decode step and of the prefill by
 class of kernel (launched one by one behind a head start of other work, with
 events between the classes) and what each class achieves of the measured
 peak.  `--workload unequal` is the second benchmark configuration: a batch of
@@ -407,6 +408,20 @@ def main() -> int:
                     n_e2e = min(args.e2e_steps, args.context - args.prompt - e2e_warmup - 2)
                     prompts = [torch.randint(0, V, (e2e_prompt(n_e2e),), generator=gen).tolist() for _ in range(b)]
                     points[f"e2e_b{b}"] = round(e2e_run(prompts, n_e2e)[0], 1)
+            if not args.no_e2e:
+                # time to the first token of one request, host to host (the reference's tables quote it for a
+                # short chat prompt, BENCHMARK.md:186-194): a 32-token and a 2,048-token prompt, best of five
+                for n in (32, 2048):
+                    if n + 2 > args.context:
+                        continue
+                    best = float("inf")
+                    for _ in range(6):
+                        prompt = torch.randint(0, V, (n,), generator=gen).tolist()
+                        torch.cuda.synchronize()
+                        t0 = time.perf_counter()
+                        engine.generate([prompt], tq.GenerationParams.greedy(1, stop_token_ids=()))
+                        best = min(best, time.perf_counter() - t0)
+                    points[f"ttft_ms_p{n}"] = round(best * 1e3, 3)
             rec["points"] = points
 
     if not args.no_kernels:

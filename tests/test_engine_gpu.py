@@ -385,3 +385,30 @@ def test_a_step_that_fails_after_reserving_gives_its_pages_back(tmp_root, monkey
     got = eng.step([StepRow(s, toks[10:150], [139])])
     assert_close(got, plain_logits(folder, toks)[149:150], "float32", "after a failed step")
     eng.release(s)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_single_prompts_replayed_as_padded_graphs(tmp_root, name, dtype):
+    """A single prompt from position 0 with one wanted row is padded with rows of token 0 to a multiple of 64
+    and replayed as a captured graph (the second prompt of a padded size is a replay).  The padding changes no
+    result: the logits equal the plain implementation's, the cache holds the real tokens only (pages, length),
+    and tokens decoded afterwards read the right keys."""
+    from tq_kv_b200.engine import StepRow
+    eng, folder = engine_for(tmp_root, name, dtype)
+    assert eng.pad_prompts and eng.use_graphs
+    V = TINY[name]["vocab_size"]
+    pages0 = eng.cache.free_pages()
+    for rnd_seed, n in enumerate([2, 63, 64, 65, 100, 7, 128, 70, 129]):      # 64: 2, 63, 64, 7; 128: 65, 100, 128, 70
+        toks = random_tokens(n + 3, V, 500 + rnd_seed)
+        want = plain_logits(folder, toks)
+        s = eng.new_sequence()
+        got = eng.step([StepRow(s, toks[:n], [n - 1])])
+        assert_close(got, want[n - 1:n], dtype, f"padded prompt of {n} tokens")
+        assert eng.length(s) == n and eng.cache.free_pages() == pages0 - -(-n // 64)
+        after = [eng.step([StepRow(s, [t], [0])]) for t in toks[n:]]
+        assert_close(torch.cat(after), want[n:], dtype, f"decoding after a padded prompt of {n} tokens")
+        eng.release(s)
+    assert sorted(eng._prompt_graphs) == [64, 128, 192] and all(g.graph is not None for g in eng._prompt_graphs.values())
+    eng.check_status()
+    eng.cache.book.check()
+    assert eng.cache.free_pages() == pages0

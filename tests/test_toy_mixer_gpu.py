@@ -156,6 +156,7 @@ def test_a_stateful_mixer_in_replayed_graphs_advances_its_state_once_per_step(tm
         for graphs in (True, False):
             eng = Engine.from_folder(folder, dtype="float32", max_tokens=512, max_slots=3)
             assert eng.use_graphs                       # the toy part declares itself capturable
+            assert not eng.pad_prompts                  # but not that padded rows are harmless (it keeps state)
             eng.use_graphs = graphs
             slots = [eng.new_sequence() for _ in reqs]
             cut = [6, 4, 5]

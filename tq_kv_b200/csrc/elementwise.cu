@@ -174,6 +174,9 @@ TQ_API int tq_rmsnorm(const float* x, const float* w, void* out, int out_dtype, 
 // logical page p / page_tokens (modulo ring_pages if > 0) at row
 // p % page_tokens.  In a ring, only the last ring_pages*page_tokens positions
 // of a sequence are written, so that no two tokens of one step meet in a row.
+// A row whose position is not below new_lens of its sequence is padding (a
+// prompt padded to the size of a captured graph): it gets q (and packed k, v)
+// like any row and leaves the cache alone.
 // ---------------------------------------------------------------------------
 template <typename TI, typename TC>
 __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* __restrict__ bias,
@@ -200,9 +203,9 @@ __global__ void qkv_rope_cache_kernel(const TI* __restrict__ qkv, const float* _
     TC* cache = nullptr;
     if (!is_q && k_pages != nullptr) {
         int lp = pos / page_tokens;
-        bool keep = true;
+        bool keep = pos < new_lens[b];          // a row past its sequence's new length is padding: nothing is cached
         if (ring_pages > 0) {
-            keep = pos >= new_lens[b] - ring_pages * page_tokens;
+            keep = keep && pos >= new_lens[b] - ring_pages * page_tokens;
             lp %= ring_pages;
         }
         if (keep) {
@@ -278,7 +281,7 @@ qkv_rope_cache_vec_kernel(const float* __restrict__ qkv, const float* __restrict
     const float* cs = cos_tab + (size_t)pos * half;
     const float* sn = sin_tab + (size_t)pos * half;
     size_t cache_row = 0;
-    bool to_cache = k_pages != nullptr;
+    bool to_cache = k_pages != nullptr && pos < new_lens[b];       // (rows past the new length are padding)
     if (to_cache) {
         int lp = pos / page_tokens;
         if (ring_pages > 0) {

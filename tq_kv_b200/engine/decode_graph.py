@@ -136,3 +136,107 @@ class DecodeGraph:
         self.graph.replay()
         kernels.launches[0] += self.kernels_per_replay
         return self.logits.clone() if keep else self.logits
+
+
+class PromptGraph:
+    """The prompt of ONE sequence from position 0, as a replayed CUDA graph.
+
+    A short prompt is a few hundred kernels of a few microseconds each: launched from Python one by one, the
+    host sets the pace (a 32-token prompt of a small model takes ten times its device time).  The step is
+    therefore padded with rows of token 0 to a multiple of PAD tokens and captured once per padded size over
+    static buffers, as decode steps are per batch size.  Padded rows change nothing that lasts: causal
+    attention lets no real row see them, every other part works row by row, and the rotary kernel caches only
+    rows below the sequence's new length (`new_lens`, which holds the real one).  Pages are reserved and
+    lengths committed for the real tokens only.  The engine takes this path only for models whose parts all
+    say `padded_rows_ok`, with no per-sequence state, and for one wanted row."""
+    PAD = 64
+    MAX_TOKENS = 2048          # longer prompts are bound by the device, not by their launches
+    RING = 2
+
+    def __init__(self, model, cache: SequenceCache, sampled_ids: torch.Tensor, runtime, T_pad: int, pool=None):
+        self.model, self.cache, self.sampled_ids, self.T = model, cache, sampled_ids, T_pad
+        dev = runtime.device
+        self.widths = []
+        for g in cache.groups:
+            full = -(-runtime.max_context // g.book.page_tokens)
+            self.widths.append(min(full, g.book.ring_pages) if g.book.ring_pages else full)
+        T = T_pad
+        seg = [T, T, T, 2, 1, 1, 1, 1, T] + list(self.widths)
+        self.offs, total = [], 0
+        for s in seg:
+            self.offs.append(total)
+            total += _pad4(s)
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        self.host = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.events = [None] * self.RING
+        self.turn = 0
+        o = self.offs
+        for h in self.host:                                   # what never changes
+            a = h.numpy()
+            a[o[2]:o[2] + T] = np.arange(T, dtype=np.int32)   # tok_pos: the sequence starts at 0
+            a[o[3] + 1] = T                                   # cu_seqlens = [0, T]
+            a[o[8]:o[8] + T] = -1                             # no token comes from the sampler's ids
+        d = self.dev
+
+        def seg_view(i, n):
+            return d[o[i]:o[i] + n]
+
+        self.batch = StepBatch(
+            n_tokens=T, n_seqs=1, tokens=seg_view(0, T), tok_seq=seg_view(1, T), tok_pos=seg_view(2, T),
+            cu_seqlens=seg_view(3, 2), slots=seg_view(4, 1), start_pos=seg_view(5, 1), new_lens=seg_view(6, 1),
+            logit_rows=seg_view(7, 1), n_logit_rows=1,
+            block_tables=[(seg_view(9 + gi, w), w) for gi, w in enumerate(self.widths)],
+            host_slots=[0], host_start=[0], host_lens=[T], packed_bytes=total * 4, tok_src=seg_view(8, T),
+            any_source=False)
+        self.pool = pool
+        self.graph = None
+        self.logits = None
+        self.kernels_per_replay = 0
+
+    def _fill(self, row) -> None:
+        i = self.turn % self.RING
+        self.turn += 1
+        if self.events[i] is not None:
+            self.events[i].synchronize()                      # the copy that last used this buffer is done
+        h = self.host[i]
+        a, o, n = h.numpy(), self.offs, len(row.tokens)
+        a[o[0]:o[0] + n] = row.tokens
+        a[o[0] + n:o[0] + self.T] = 0                         # the padding
+        a[o[4]] = row.slot
+        a[o[6]] = n                                           # the real length: rows from n on are not cached
+        a[o[7]] = row.want[0]
+        for gi in range(len(self.widths)):
+            pages = self.cache.book.pages(gi, row.slot)
+            a[o[9 + gi]:o[9 + gi] + len(pages)] = pages
+        self.batch.host_slots = [row.slot]
+        self.dev.copy_(h, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+    def run(self, row) -> torch.Tensor:
+        """Runs the prompt `row` (pages reserved, nothing cached yet); returns float32 logits [1, vocab]."""
+        from .. import kernels
+        self._fill(row)
+        if self.graph is None:
+            # first use: once kernel by kernel, then captured for the prompts to come (see DecodeGraph.run)
+            n0 = kernels.launches[0]
+            logits = forward_step(self.model, self.cache, self.sampled_ids, self.batch)
+            self.kernels_per_replay = kernels.launches[0] - n0
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g, pool=self.pool):
+                    self.logits = forward_step(self.model, self.cache, self.sampled_ids, self.batch)
+            finally:
+                if gc_was_on:
+                    gc.enable()
+            kernels.launches[0] -= self.kernels_per_replay     # capturing launched nothing
+            self.graph = g
+            return logits
+        self.graph.replay()
+        kernels.launches[0] += self.kernels_per_replay
+        return self.logits.clone()

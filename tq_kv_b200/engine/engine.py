@@ -23,7 +23,7 @@ from ..parts import Runtime
 from ..weights import load_tensors, random_tensors
 from ..weights.random_init import storage_dtype
 from .batch import FlatRows, StepRow, build_step_batch
-from .decode_graph import DecodeGraph, forward_step
+from .decode_graph import DecodeGraph, PromptGraph, forward_step
 from .readback import SampledIds
 from .model import DecoderModel
 
@@ -47,6 +47,10 @@ class Engine:
         self.steps_run = 0
         self.use_graphs = model.graph_capturable      # replay captured CUDA graphs for decode steps
         self._decode_graphs: dict[int, "DecodeGraph"] = {}
+        # single prompts from position 0 replay graphs too, padded to a few sizes (PromptGraph)
+        self.pad_prompts = model.padded_rows_ok and not cache.state
+        self._prompt_graphs: dict[int, "PromptGraph"] = {}
+        self._prompt_pool = None
         self.h2d_bytes = 0            # bytes of step inputs copied to the device so far
         self.sampled = SampledIds(runtime.device)     # where the sampler's ids go; rows may name them as source
 
@@ -173,6 +177,19 @@ class Engine:
                     logits = graph.run(rows, keep_logits)
                     self.h2d_bytes += graph.batch.packed_bytes
                     kernels.mark_tc_launched()      # read with the sampled ids, or by check_status()
+                elif self._prompt_graph_takes(rows, lens):
+                    T_pad = -(-int(lens[0]) // PromptGraph.PAD) * PromptGraph.PAD
+                    graph = self._prompt_graphs.get(T_pad)
+                    if graph is None:
+                        if self._prompt_pool is None:
+                            self._prompt_pool = torch.cuda.graph_pool_handle()     # one pool: they never run together
+                        graph = self._prompt_graphs[T_pad] = PromptGraph(
+                            self.model, self.cache, self.sampled.ids, self.runtime, T_pad, self._prompt_pool)
+                    logits = graph.run(rows[0])
+                    self.h2d_bytes += graph.batch.packed_bytes
+                    kernels.mark_tc_launched()
+                    if check:
+                        kernels.check_tc_status()
                 else:
                     batch = build_step_batch(rows, self.cache, self.runtime.device, flat)
                     logits = self._forward(batch)
@@ -185,6 +202,16 @@ class Engine:
         self.cache.commit(slots, lens)
         self.steps_run += 1
         return logits
+
+    def _prompt_graph_takes(self, rows, lens) -> bool:
+        """Whether the step is one whole prompt that may run as a padded, replayed graph (PromptGraph)."""
+        if not (self.use_graphs and self.pad_prompts and len(rows) == 1):
+            return False
+        r, n = rows[0], int(lens[0])
+        if r.source is not None or len(r.want) != 1 or self.cache.length(r.slot) != 0:
+            return False
+        T_pad = -(-n // PromptGraph.PAD) * PromptGraph.PAD
+        return n > 1 and T_pad <= min(PromptGraph.MAX_TOKENS, self.runtime.max_context) and kernels._lib.timeline is None
 
     def check_status(self) -> None:
         """Raises if a kernel of an earlier step gave up on a bounded wait

@@ -44,6 +44,12 @@ class DecoderModel:
     def graph_capturable(self) -> bool:
         return all(getattr(p, "graph_capturable", True) for p in self._all_parts())
 
+    @property
+    def padded_rows_ok(self) -> bool:
+        """Whether a step may carry padded rows (see Part.padded_rows_ok): every part and block says so."""
+        return (all(getattr(p, "padded_rows_ok", False) for p in self._all_parts())
+                and all(getattr(b, "padded_rows_ok", False) for b in self.blocks))
+
     def weight_specs(self) -> dict[str, WeightSpec]:
         """Every tensor the model expects, by name.  Two parts may name the
         same tensor (a tied head) if they agree on its shape."""

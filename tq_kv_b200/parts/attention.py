@@ -23,6 +23,7 @@ from .registry import make_part
 
 class GQAttention(Mixer):
     takes_pending_norm = True           # x goes to kernels.linear only
+    padded_rows_ok = True               # causal: no row sees a later one; the rotary kernel caches real rows only
     ZERO_BUFFER_ROWS = 64               # decode steps of up to this many rows use the shared q/k/v buffer
 
     def __init__(self, spec):

@@ -109,6 +109,11 @@ class Part:
     # it) sets this to False; the engine then launches that model's decode
     # steps kernel by kernel instead of replaying a captured CUDA graph.
     graph_capturable = True
+    # A step may carry rows beyond a sequence's real tokens (a prompt padded to the size of a captured graph; the
+    # batch's new_lens holds the real length).  A part that says True treats rows independently, or — a mixer —
+    # lets no real row see a padded one and writes nothing lasting for padded rows.  The engine pads only if
+    # every part of the model says so.
+    padded_rows_ok = False
     # A mixer or feed-forward that hands its input to `kernels.linear` and reads it nowhere else may set this:
     # the block then passes the norm before it as a `kernels.PendingNorm`, which the product can fold in.
     takes_pending_norm = False

@@ -16,6 +16,8 @@ from .registry import make_part
 
 
 class PrenormResidualBlock:
+    padded_rows_ok = True               # as far as its parts are
+
     def __init__(self, spec: LayerSpec):
         self.spec = spec
         self.mixer_norm = make_part(spec.part("mixer_norm"))

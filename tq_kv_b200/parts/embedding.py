@@ -15,6 +15,8 @@ from .base import Part, Runtime, WeightSpec
 
 
 class TokenEmbedding(Part):
+    padded_rows_ok = True               # row by row
+
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(self.params["vocab_size"])
@@ -36,6 +38,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    padded_rows_ok = True               # row by row
+
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(self.params["vocab_size"])

@@ -11,6 +11,7 @@ from .base import FeedForward, Runtime, StepContext, WeightSpec
 
 class SwiGLU(FeedForward):
     takes_pending_norm = True           # x goes to kernels.linear only
+    padded_rows_ok = True               # row by row
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -11,6 +11,8 @@ from .base import Norm, Runtime, WeightSpec, float32_vector
 
 
 class RMSNorm(Norm):
+    padded_rows_ok = True               # row by row
+
     def __init__(self, spec):
         super().__init__(spec)
         self.width = int(self.params["width"])

@@ -17,6 +17,8 @@ from .base import PositionEncoding, Runtime, StepContext
 
 
 class RotaryHalved(PositionEncoding):
+    padded_rows_ok = True               # rows at or past their sequence's new length are not cached
+
     def __init__(self, spec):
         super().__init__(spec)
         self.head_dim = int(self.params["head_dim"])
