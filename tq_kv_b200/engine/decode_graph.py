@@ -1,4 +1,4 @@
-"""Decode steps as replayed CUDA graphs.
+"""Decode steps, and single prompts, as replayed CUDA graphs (DecodeGraph, PromptGraph).
 
 A decode step of B sequences launches a few hundred small kernels; launching
 them from Python costs more than running them.  For each batch size the step
