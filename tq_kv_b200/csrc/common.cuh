@@ -153,7 +153,8 @@ static inline bool tq_deterministic() {
 // then has nothing to gain, is left out of the default.  TQ_PDL=0 switches it off,
 // TQ_PDL=1 on for every family, a larger number is a mask of families:
 // 2 element-wise, 4 skinny_gemm, 8 decode_gemm_tc, 16 flash_decode,
-// 32 attention merge, 64 sampling.  Every launch names its family.
+// 32 attention merge, 64 sampling, 128 the many-row product (gemm_tc), 256 the prompt attention.  Every launch
+// names its family.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
@@ -163,7 +164,10 @@ __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.laun
 #define TQ_PDL_FLASH_DECODE 16
 #define TQ_PDL_MERGE 32
 #define TQ_PDL_SAMPLING 64
-#define TQ_PDL_DEFAULT (TQ_PDL_ELEMENTWISE | TQ_PDL_SKINNY | TQ_PDL_DECODE_GEMM | TQ_PDL_FLASH_DECODE | TQ_PDL_SAMPLING)
+#define TQ_PDL_GEMM_TC 128
+#define TQ_PDL_PREFILL_ATTENTION 256
+#define TQ_PDL_DEFAULT (TQ_PDL_ELEMENTWISE | TQ_PDL_SKINNY | TQ_PDL_DECODE_GEMM | TQ_PDL_FLASH_DECODE | TQ_PDL_SAMPLING | \
+                        TQ_PDL_GEMM_TC | TQ_PDL_PREFILL_ATTENTION)
 static inline bool tq_pdl_enabled(int family) {
     static int mask = -1;
     if (mask < 0) {

@@ -231,6 +231,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_s = *tmem_slot;                    // S: two buffers of 64 columns
     const uint32_t tmem_o = tmem_s + 128;                  // O: columns 128..128+HD, accumulated over the tiles
+    // Programmatic dependent launch (common.cuh): q, k and v come from the kernel before; the step's lengths
+    // and tables, read above, were copied in before its first kernel.
+    pdl_wait();
+    pdl_launch();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -453,10 +457,9 @@ static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
         configured = true;
     }
     const dim3 grid(nh, (n_tokens + FT_BM - 1) / FT_BM + n_seqs);
-    flash_prefill_tc_kernel<HD, PAGED><<<grid, FT_THREADS, SMEM, stream>>>(
-        mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, start_pos, n_seqs, window,
-        scale * 1.4426950408889634f, out, nh, nkv, status);
-    return tq_launch_status();
+    return tq_launch_pdl(TQ_PDL_PREFILL_ATTENTION, flash_prefill_tc_kernel<HD, PAGED>, grid, dim3(FT_THREADS), SMEM, stream,
+                         mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, start_pos, n_seqs, window,
+                         scale * 1.4426950408889634f, out, nh, nkv, status);
 }
 
 // q, out [T, nh * hd] bfloat16.  Keys/values: packed [T, nkv * hd] (every

@@ -273,6 +273,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch (common.cuh): barriers and tensor memory are set up under the tail of the
+    // kernel before; its results (A, and C where the product adds to it) are touched only from here on.
+    pdl_wait();
+    pdl_launch();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -475,6 +479,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     cluster_sync_all();                                    // the peer's barriers exist from here on
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                                            // (as in the single-SM form)
+    pdl_launch();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -628,9 +634,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     if (parts > 1) n_whole = n_tiles - n_tiles % sm_count;
     const int n_items = n_whole + (n_tiles - n_whole) * parts;
     const int grid = n_items < sm_count ? n_items : sm_count;
-    gemm_tc_kernel<EPI, TO><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(ma, mb, mc, bias, M, N, K, b_rows_second,
-                                                                        n_whole, parts, status);
-    return tq_launch_status();
+    return tq_launch_pdl(TQ_PDL_GEMM_TC, gemm_tc_kernel<EPI, TO>, dim3(grid), dim3(TC_THREADS), TC_SMEM_BYTES, stream, ma, mb,
+                         mc, bias, M, N, K, b_rows_second, n_whole, parts, status);
 }
 
 // The pair form: 256-row tiles on clusters of two blocks.
@@ -652,9 +657,8 @@ static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CU
     if (parts > 1) n_whole = n_tiles - n_tiles % pairs;
     const int n_items = n_whole + (n_tiles - n_whole) * parts;
     const int grid = 2 * (n_items < pairs ? n_items : pairs);
-    gemm_tc_pair_kernel<EPI, TO><<<grid, TC_THREADS, T2_SMEM_BYTES, stream>>>(ma, mb, mc, bias, M, N, K, b_rows_second,
-                                                                             n_whole, parts, status);
-    return tq_launch_status();
+    return tq_launch_pdl(TQ_PDL_GEMM_TC, gemm_tc_pair_kernel<EPI, TO>, dim3(grid), dim3(TC_THREADS), T2_SMEM_BYTES, stream,
+                         ma, mb, mc, bias, M, N, K, b_rows_second, n_whole, parts, status);
 }
 
 // 0: pairs of SMs for products of more than 128 rows, single SMs otherwise; 1: single SMs always; 2: pairs always.
