@@ -12,7 +12,8 @@ as host token ids and every step's token ids come back to the host (the loop
 reads them one step late, while the device runs the next step); it runs for
 at least 128 timed steps whatever K is, after warm-up steps as the device-timed
 run has them (`e2e.steps`, `e2e.warmup`).  `prefill`
-is one step over a 2,048-token prompt; `roofline` relates the decode step's
+is one step over a 2,048-token prompt (timed the second time: like every single prompt from position 0 it then
+replays the graph captured the first time, the same kernels without the host's launches between them); `roofline` relates the decode step's
 necessary bytes (every weight it uses once, the cache of the live sequences)
 to its time; `points` hold decode at batch 1 and 64, device-timed and end to
 end, and the time to the first token of a 32- and a 2,048-token prompt through
