@@ -408,7 +408,36 @@ def test_single_prompts_replayed_as_padded_graphs(tmp_root, name, dtype):
         after = [eng.step([StepRow(s, [t], [0])]) for t in toks[n:]]
         assert_close(torch.cat(after), want[n:], dtype, f"decoding after a padded prompt of {n} tokens")
         eng.release(s)
-    assert sorted(eng._prompt_graphs) == [64, 128, 192] and all(g.graph is not None for g in eng._prompt_graphs.values())
+    assert sorted(eng._prompt_graphs) == [(1, 64), (1, 128), (1, 192)]
+    assert all(g.graph is not None for g in eng._prompt_graphs.values())
+    eng.check_status()
+    eng.cache.book.check()
+    assert eng.cache.free_pages() == pages0
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_several_prompts_replayed_as_one_padded_graph(tmp_root, name, dtype):
+    """Prompts of several sequences in one step replay a graph captured per (number of sequences, padded number
+    of tokens); how the tokens divide among the sequences is data.  Three steps of three prompts with the same
+    padded size and different lengths (the second and third are replays), each against the plain implementation,
+    then one decoded token per sequence from what the prompts cached."""
+    from tq_kv_b200.engine import StepRow
+    eng, folder = engine_for(tmp_root, name, dtype)
+    V = TINY[name]["vocab_size"]
+    pages0 = eng.cache.free_pages()
+    for k, lens in enumerate([(40, 9, 70), (5, 100, 20), (63, 1, 64), (30, 31)]):       # 119, 125, 128 -> 128; 61 -> 64
+        reqs = [random_tokens(n + 1, V, 900 + 10 * k + i) for i, n in enumerate(lens)]
+        wants = [plain_logits(folder, t) for t in reqs]
+        slots = [eng.new_sequence() for _ in reqs]
+        got = eng.step([StepRow(s, t[:-1], [len(t) - 2]) for s, t in zip(slots, reqs)])
+        assert_close(got, torch.stack([w[-2] for w in wants]), dtype, f"prompts of {lens} tokens in one padded step")
+        assert [eng.length(s) for s in slots] == list(lens)
+        assert eng.cache.free_pages() == pages0 - sum(-(-n // 64) for n in lens)
+        nxt = eng.step([StepRow(s, [t[-1]], [0]) for s, t in zip(slots, reqs)])
+        assert_close(nxt, torch.stack([w[-1] for w in wants]), dtype, f"decoding after prompts of {lens} tokens")
+        for s in slots:
+            eng.release(s)
+    assert (3, 128) in eng._prompt_graphs and (2, 64) in eng._prompt_graphs
     eng.check_status()
     eng.cache.book.check()
     assert eng.cache.free_pages() == pages0

@@ -139,29 +139,34 @@ class DecodeGraph:
 
 
 class PromptGraph:
-    """The prompt of ONE sequence from position 0, as a replayed CUDA graph.
+    """Whole prompts of B sequences from position 0, as a replayed CUDA graph.
 
     A short prompt is a few hundred kernels of a few microseconds each: launched from Python one by one, the
     host sets the pace (a 32-token prompt of a small model takes ten times its device time).  The step is
-    therefore padded with rows of token 0 to a multiple of PAD tokens and captured once per padded size over
-    static buffers, as decode steps are per batch size.  Padded rows change nothing that lasts: causal
-    attention lets no real row see them, every other part works row by row, and the rotary kernel caches only
-    rows below the sequence's new length (`new_lens`, which holds the real one).  Pages are reserved and
-    lengths committed for the real tokens only.  The engine takes this path only for models whose parts all
-    say `padded_rows_ok`, with no per-sequence state, and for one wanted row."""
+    therefore padded with rows of token 0 (they continue the last sequence) to a multiple of PAD tokens and
+    captured once per (number of sequences, padded size) over static buffers, as decode steps are per batch
+    size; how the tokens divide among the sequences is data (cu_seqlens), not part of the capture.  Padded
+    rows change nothing that lasts: causal attention lets no real row see them, every other part works row by
+    row, and the rotary kernel caches only rows below their sequence's new length (`new_lens`, which holds the
+    real one).  Pages are reserved and lengths committed for the real tokens only.  The engine takes this path
+    only for models whose parts all say `padded_rows_ok`, with no per-sequence state, and for one wanted row
+    per sequence."""
     PAD = 64
-    MAX_TOKENS = 2048          # longer prompts are bound by the device, not by their launches
+    MAX_TOKENS = 2048          # longer steps are bound by the device, not by their launches
+    MAX_ROWS = 16
+    MAX_GRAPHS = 96            # captured graphs an engine keeps (every size of a single prompt, and some more)
     RING = 2
 
-    def __init__(self, model, cache: SequenceCache, sampled_ids: torch.Tensor, runtime, T_pad: int, pool=None):
-        self.model, self.cache, self.sampled_ids, self.T = model, cache, sampled_ids, T_pad
+    def __init__(self, model, cache: SequenceCache, sampled_ids: torch.Tensor, runtime, B: int, T_pad: int,
+                 pool=None):
+        self.model, self.cache, self.sampled_ids, self.B, self.T = model, cache, sampled_ids, B, T_pad
         dev = runtime.device
         self.widths = []
         for g in cache.groups:
             full = -(-runtime.max_context // g.book.page_tokens)
             self.widths.append(min(full, g.book.ring_pages) if g.book.ring_pages else full)
         T = T_pad
-        seg = [T, T, T, 2, 1, 1, 1, 1, T] + list(self.widths)
+        seg = [T, T, T, B + 1, B, B, B, B, T] + [B * w for w in self.widths]
         self.offs, total = [], 0
         for s in seg:
             self.offs.append(total)
@@ -173,8 +178,6 @@ class PromptGraph:
         o = self.offs
         for h in self.host:                                   # what never changes
             a = h.numpy()
-            a[o[2]:o[2] + T] = np.arange(T, dtype=np.int32)   # tok_pos: the sequence starts at 0
-            a[o[3] + 1] = T                                   # cu_seqlens = [0, T]
             a[o[8]:o[8] + T] = -1                             # no token comes from the sampler's ids
         d = self.dev
 
@@ -182,42 +185,51 @@ class PromptGraph:
             return d[o[i]:o[i] + n]
 
         self.batch = StepBatch(
-            n_tokens=T, n_seqs=1, tokens=seg_view(0, T), tok_seq=seg_view(1, T), tok_pos=seg_view(2, T),
-            cu_seqlens=seg_view(3, 2), slots=seg_view(4, 1), start_pos=seg_view(5, 1), new_lens=seg_view(6, 1),
-            logit_rows=seg_view(7, 1), n_logit_rows=1,
-            block_tables=[(seg_view(9 + gi, w), w) for gi, w in enumerate(self.widths)],
-            host_slots=[0], host_start=[0], host_lens=[T], packed_bytes=total * 4, tok_src=seg_view(8, T),
-            any_source=False)
+            n_tokens=T, n_seqs=B, tokens=seg_view(0, T), tok_seq=seg_view(1, T), tok_pos=seg_view(2, T),
+            cu_seqlens=seg_view(3, B + 1), slots=seg_view(4, B), start_pos=seg_view(5, B), new_lens=seg_view(6, B),
+            logit_rows=seg_view(7, B), n_logit_rows=B,
+            block_tables=[(seg_view(9 + gi, B * w), w) for gi, w in enumerate(self.widths)],
+            host_slots=[0] * B, host_start=[0] * B, host_lens=[T] * B, packed_bytes=total * 4,      # (lengths: an upper bound)
+            tok_src=seg_view(8, T), any_source=False)
         self.pool = pool
         self.graph = None
         self.logits = None
         self.kernels_per_replay = 0
 
-    def _fill(self, row) -> None:
+    def _fill(self, rows) -> None:
         i = self.turn % self.RING
         self.turn += 1
         if self.events[i] is not None:
             self.events[i].synchronize()                      # the copy that last used this buffer is done
         h = self.host[i]
-        a, o, n = h.numpy(), self.offs, len(row.tokens)
-        a[o[0]:o[0] + n] = row.tokens
-        a[o[0] + n:o[0] + self.T] = 0                         # the padding
-        a[o[4]] = row.slot
-        a[o[6]] = n                                           # the real length: rows from n on are not cached
-        a[o[7]] = row.want[0]
-        for gi in range(len(self.widths)):
-            pages = self.cache.book.pages(gi, row.slot)
-            a[o[9 + gi]:o[9 + gi] + len(pages)] = pages
-        self.batch.host_slots = [row.slot]
+        a, o, B, T = h.numpy(), self.offs, self.B, self.T
+        at = 0
+        for b, r in enumerate(rows):
+            n = len(r.tokens)
+            last = b == B - 1
+            end = T if last else at + n                       # the padding continues the last sequence
+            a[o[0] + at:o[0] + at + n] = r.tokens
+            a[o[0] + at + n:o[0] + end] = 0
+            a[o[1] + at:o[1] + end] = b
+            a[o[2] + at:o[2] + end] = np.arange(end - at, dtype=np.int32)
+            a[o[3] + b + 1] = end
+            a[o[4] + b] = r.slot
+            a[o[6] + b] = n                                   # the real length: rows from n on are not cached
+            a[o[7] + b] = at + r.want[0]
+            for gi, w in enumerate(self.widths):
+                pages = self.cache.book.pages(gi, r.slot)
+                a[o[9 + gi] + b * w:o[9 + gi] + b * w + len(pages)] = pages
+            at = end
+        self.batch.host_slots = [r.slot for r in rows]
         self.dev.copy_(h, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
 
-    def run(self, row) -> torch.Tensor:
-        """Runs the prompt `row` (pages reserved, nothing cached yet); returns float32 logits [1, vocab]."""
+    def run(self, rows) -> torch.Tensor:
+        """Runs the prompts `rows` (pages reserved, nothing cached yet); returns float32 logits [B, vocab]."""
         from .. import kernels
-        self._fill(row)
+        self._fill(rows)
         if self.graph is None:
             # first use: once kernel by kernel, then captured for the prompts to come (see DecodeGraph.run)
             n0 = kernels.launches[0]

@@ -49,7 +49,7 @@ class Engine:
         self._decode_graphs: dict[int, "DecodeGraph"] = {}
         # single prompts from position 0 replay graphs too, padded to a few sizes (PromptGraph)
         self.pad_prompts = model.padded_rows_ok and not cache.state
-        self._prompt_graphs: dict[int, "PromptGraph"] = {}
+        self._prompt_graphs: dict[tuple, "PromptGraph"] = {}
         self._prompt_pool = None
         self.h2d_bytes = 0            # bytes of step inputs copied to the device so far
         self.sampled = SampledIds(runtime.device)     # where the sampler's ids go; rows may name them as source
@@ -178,14 +178,14 @@ class Engine:
                     self.h2d_bytes += graph.batch.packed_bytes
                     kernels.mark_tc_launched()      # read with the sampled ids, or by check_status()
                 elif self._prompt_graph_takes(rows, lens):
-                    T_pad = -(-int(lens[0]) // PromptGraph.PAD) * PromptGraph.PAD
-                    graph = self._prompt_graphs.get(T_pad)
+                    key = (len(rows), -(-int(lens.sum()) // PromptGraph.PAD) * PromptGraph.PAD)
+                    graph = self._prompt_graphs.get(key)
                     if graph is None:
                         if self._prompt_pool is None:
                             self._prompt_pool = torch.cuda.graph_pool_handle()     # one pool: they never run together
-                        graph = self._prompt_graphs[T_pad] = PromptGraph(
-                            self.model, self.cache, self.sampled.ids, self.runtime, T_pad, self._prompt_pool)
-                    logits = graph.run(rows[0])
+                        graph = self._prompt_graphs[key] = PromptGraph(
+                            self.model, self.cache, self.sampled.ids, self.runtime, key[0], key[1], self._prompt_pool)
+                    logits = graph.run(rows)
                     self.h2d_bytes += graph.batch.packed_bytes
                     kernels.mark_tc_launched()
                     if check:
@@ -204,14 +204,22 @@ class Engine:
         return logits
 
     def _prompt_graph_takes(self, rows, lens) -> bool:
-        """Whether the step is one whole prompt that may run as a padded, replayed graph (PromptGraph)."""
-        if not (self.use_graphs and self.pad_prompts and len(rows) == 1):
+        """Whether the step is whole prompts that may run as a padded, replayed graph (PromptGraph)."""
+        if not (self.use_graphs and self.pad_prompts and len(rows) <= PromptGraph.MAX_ROWS):
             return False
-        r, n = rows[0], int(lens[0])
-        if r.source is not None or len(r.want) != 1 or self.cache.length(r.slot) != 0:
+        if kernels._lib.timeline is not None:
             return False
-        T_pad = -(-n // PromptGraph.PAD) * PromptGraph.PAD
-        return n > 1 and T_pad <= min(PromptGraph.MAX_TOKENS, self.runtime.max_context) and kernels._lib.timeline is None
+        for r in rows:
+            if r.source is not None or len(r.want) != 1:
+                return False
+        T_pad = -(-int(lens.sum()) // PromptGraph.PAD) * PromptGraph.PAD
+        if int(lens.max()) < 2 or T_pad > min(PromptGraph.MAX_TOKENS, self.runtime.max_context):
+            return False
+        if any(self.cache.book.lengths([r.slot for r in rows])):
+            return False                                   # a continuation: its keys come from the pages
+        # every size of a single prompt may be captured; of the others as many as the engine keeps room for
+        return (len(rows), T_pad) in self._prompt_graphs or len(rows) == 1 \
+            or len(self._prompt_graphs) < PromptGraph.MAX_GRAPHS - PromptGraph.MAX_TOKENS // PromptGraph.PAD
 
     def check_status(self) -> None:
         """Raises if a kernel of an earlier step gave up on a bounded wait
